@@ -1,0 +1,124 @@
+/*
+ * b200lm.h — C ABI of the B200 LlmExecutor backend for LiteRT-LM.
+ *
+ * The library (libb200lm.so) replaces, for one decoder model on one B200, the
+ * work the reference does inside LlmLiteRtCompiledModelExecutor:
+ * Prefill / Decode / DecodeLogits with the same token hold-back, step counting
+ * and bucketed work groups, on hand-written sm_100a CUDA kernels.
+ *
+ * Conventions (those of the reference's one dynamic C boundary, the GPU
+ * sampler in runtime/components/sampler_factory.cc:30-57):
+ *   - every call returns an absl::StatusCode integer (0 OK, 1 Cancelled,
+ *     3 InvalidArgument, 4 DeadlineExceeded, 5 NotFound, 9 FailedPrecondition,
+ *     12 Unimplemented, 13 Internal);
+ *   - on failure *err (when err != NULL) receives a malloc'd message that the
+ *     caller releases with free();
+ *   - handles are opaque; one handle is used from one thread at a time (the
+ *     reference drives an executor from a single engine worker thread,
+ *     runtime/core/engine_impl.cc:185-186); different handles are independent.
+ * There is no CPU fallback: without a CUDA device every entry point that needs
+ * one fails with FailedPrecondition.
+ */
+#ifndef B200LM_H_
+#define B200LM_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct B200LmExecutor B200LmExecutor;
+
+enum { B200LM_DECODE_AUTO = 0, B200LM_DECODE_PHASE_KERNELS = 1, B200LM_DECODE_PERSISTENT = 2 };
+enum { B200LM_GEMM_AUTO = 0, B200LM_GEMM_CHECK = 1, B200LM_GEMM_TCGEN05 = 2 };
+
+typedef struct B200LmConfig {
+  int32_t struct_size;     /* sizeof(B200LmConfig), for forward compatibility */
+  int32_t device;          /* CUDA device ordinal */
+  int32_t max_num_tokens;  /* KV capacity; 0 = the model's context length.
+                              Counterpart of LlmExecutorSettings::GetMaxNumTokens
+                              (runtime/executor/llm_executor_settings.h:95-154). */
+  int32_t decode_mode;     /* B200LM_DECODE_* */
+  int32_t prefill_gemm;    /* B200LM_GEMM_* */
+  int32_t reserved0;
+  void* stream;            /* cudaStream_t to run on, or NULL for an own stream */
+} B200LmConfig;
+
+/* Replaces LlmLiteRtCompiledModelExecutor::Create
+ * (runtime/executor/llm_litert_compiled_model_executor.cc:590-833): reads the
+ * `.litertlm` image (bytes, or a file path when bytes == NULL), repacks the
+ * int4 weights for the kernels and allocates the paged KV cache. */
+int B200Lm_Create(const B200LmConfig* config, const void* litertlm_bytes, uint64_t n_bytes,
+                  const char* path_or_null, B200LmExecutor** out, char** err);
+
+/* A second executor (own KV cache, own step counter) over the weights of an
+ * existing one: independent sessions on one GPU share one weight copy.  No
+ * counterpart in the reference, whose engine shares one executor between
+ * sessions and resets it (runtime/core/session_basic.cc:67-72). */
+int B200Lm_CreateShared(B200LmExecutor* weights_owner, const B200LmConfig* config,
+                        B200LmExecutor** out, char** err);
+
+void B200Lm_Destroy(B200LmExecutor* e);
+
+/* Replaces LlmLiteRtCompiledModelExecutor::Prefill(inputs, params)
+ * (llm_litert_compiled_model_executor.cc:90-276).  ids is host memory, batch 1.
+ * The last id of every work group is held back and consumed by the next
+ * Prefill / Decode call.  wait_for_completion and cancel carry
+ * ExecutorPrefillParams (runtime/executor/llm_executor_io_types.h:217-250);
+ * *cancel is polled between work groups -> Cancelled. */
+int B200Lm_Prefill(B200LmExecutor* e, const int32_t* ids, int32_t n_ids, int32_t wait_for_completion,
+                   const volatile int32_t* cancel_or_null, char** err);
+
+/* Replaces DecodeLogits(inputs) and Decode(inputs, logits)
+ * (llm_litert_compiled_model_executor.cc:300-534): runs one step on *id (or on
+ * the pending id when id == NULL; none pending -> InvalidArgument "No id
+ * available to be decoded.") and writes vocab floats to host_logits. */
+int B200Lm_DecodeLogits(B200LmExecutor* e, const int32_t* id_or_null, float* host_logits, char** err);
+
+/* Replaces Decode(output_tokens) (llm_litert_compiled_model_executor.cc:278-298):
+ * one step on the pending id, greedy arg-max on the device (lowest index wins
+ * ties, as std::max_element in runtime/components/sampling_cpu_util.cc:32-41),
+ * result becomes the pending id. */
+int B200Lm_DecodeToken(B200LmExecutor* e, int32_t* out_id, char** err);
+
+/* n_steps greedy steps with the arg-max fed back on the device, no host round
+ * trip per step; ids come back at the end.  Equivalent to n_steps calls of
+ * B200Lm_DecodeToken. */
+int B200Lm_DecodeTokens(B200LmExecutor* e, int32_t n_steps, int32_t* out_ids, char** err);
+
+/* Replaces Reset() (llm_litert_compiled_model_executor.cc:568-574): rewinds the
+ * counters, leaves the cache contents in place. */
+int B200Lm_Reset(B200LmExecutor* e, char** err);
+
+/* GetVocabSize (:576-586), GetCurrentStep (llm_litert_compiled_model_executor.h:95-97:
+ * processed tokens + 1 when an id is pending), GetExecutorSettings().GetMaxNumTokens(). */
+int B200Lm_GetVocabSize(B200LmExecutor* e, int32_t* out, char** err);
+int B200Lm_GetCurrentStep(B200LmExecutor* e, int32_t* out, char** err);
+int B200Lm_GetMaxNumTokens(B200LmExecutor* e, int32_t* out, char** err);
+
+/* ExecutorBackendName() (runtime/executor/llm_executor_base.h:79). */
+const char* B200Lm_BackendName(void);
+
+/* Waits for everything queued on the executor's stream; reports a device error
+ * word set by a kernel (bounded wait that gave up, token or position out of
+ * range) as DeadlineExceeded / InvalidArgument. */
+int B200Lm_Synchronize(B200LmExecutor* e, char** err);
+
+/* The work-group plan of the last Prefill: (bucket, ids) pairs as chosen by
+ * GetOptimizedPrefillWorkGroups (litert_compiled_model_executor_utils.cc:300-330). */
+int B200Lm_GetLastPrefillPlan(B200LmExecutor* e, int32_t* buckets, int32_t* lengths, int32_t capacity,
+                              int32_t* n_groups, char** err);
+
+/* Inspection: one cached K or V row (head_dim floats) and the physical page /
+ * slot the position maps to.  Used by the KV-indexing parity tests. */
+int B200Lm_ReadKvRow(B200LmExecutor* e, int32_t layer, int32_t is_v, int32_t kv_head, int32_t pos,
+                     float* out_row, int32_t* out_page, int32_t* out_slot, char** err);
+
+/* Number of kernels of this library launched on behalf of the handle so far. */
+int B200Lm_GetLaunchCount(B200LmExecutor* e, int64_t* out, char** err);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200LM_H_ */

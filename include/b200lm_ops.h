@@ -1,0 +1,66 @@
+/*
+ * b200lm_ops.h — operator-level C ABI of libb200lm.so.
+ *
+ * The reference hides its operators inside compiled_model_.Run
+ * (runtime/executor/llm_litert_compiled_model_executor.cc:271,407,522), so these
+ * entry points have no one-to-one reference symbol; each names the step of
+ * that opaque graph it stands for.  They exist for the operator parity tests
+ * and for the attention / GEMM micro-benchmarks.  All pointers are HOST
+ * memory unless a name says "dev"; the calls copy in, run the kernel, copy out.
+ * Same status-code and error-string conventions as b200lm.h.
+ */
+#ifndef B200LM_OPS_H_
+#define B200LM_OPS_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* Host-only repacks of canonical int4 rows ([n][k/2] bytes, element 2j in the
+ * low nibble) into the decode layout (16x64 mma tiles) and the tensor-core GEMM
+ * layout (128-row x 64-k blocks).  out must hold n_pad*k/2 bytes, n_pad = n
+ * rounded up to 16 (W4T) or 128 (W4G).  No GPU needed. */
+int B200LmOps_RepackW4T(const uint8_t* packed, int64_t n, int64_t k, uint8_t* out, char** err);
+int B200LmOps_RepackW4G(const uint8_t* packed, int64_t n, int64_t k, uint8_t* out, char** err);
+
+/* Bit-exact unpack gate: uploads canonical rows, repacks, and has the GPU
+ * expand the decode layout back to int8 [n][k] with the same device function
+ * the GEMV uses to address its tiles. */
+int B200LmOps_UnpackW4(int32_t device, const uint8_t* packed, int64_t n, int64_t k, int8_t* out, char** err);
+
+/* Decode GEMV (the int4 fully-connected op at batch 1..4):
+ * y[c][n] = scale[n] * sum_k W[n][k] x[c][k], x quantised to `nterms` int8 terms. */
+int B200LmOps_GemvW4(int32_t device, const uint8_t* packed, const float* scale, int64_t n, int64_t k,
+                     const float* x, int32_t ncols, int32_t nterms, int32_t kslices, float* y, char** err);
+
+/* Prefill GEMM (the int4 fully-connected op over T tokens), bf16 activations:
+ * mode B200LM_GEMM_CHECK or B200LM_GEMM_TCGEN05.  out is [T][n] fp32.
+ * repeat > 1 re-runs the kernel and, when ms_out != NULL, returns the mean
+ * device time per run in milliseconds (CUDA events). */
+int B200LmOps_GemmW4(int32_t device, int32_t mode, const uint8_t* packed, const float* scale, int64_t n,
+                     int64_t k, const float* a, int32_t t, int32_t ksplit, int32_t repeat, float* out,
+                     float* ms_out, char** err);
+
+/* Fused gate/up GEMM + GeGLU: out[T][ffn] = gelu_tanh(A Wg^T) * (A Wu^T). */
+int B200LmOps_GemmGegluW4(int32_t device, int32_t mode, const uint8_t* gate_packed, const float* gate_scale,
+                          const uint8_t* up_packed, const float* up_scale, int64_t ffn, int64_t k,
+                          const float* a, int32_t t, float* out, char** err);
+
+/* Attention against a paged cache built from k, v [S][hkv][hd] (fp32 host,
+ * stored as fp32 or bf16 pages): queries q [T][hq][hd] at positions
+ * qpos0 + i (or all at qpos0 + T - 1 ... see below), causal, optional window
+ * (window <= 0: global).  No QK-norm, no RoPE (raw q/k, as the attention-only
+ * micro-benchmark specifies).  nsplit > 1 runs the split-KV decode kernel plus
+ * the log-sum-exp combine (T is then a batch of independent single-token
+ * queries all at position S - 1); nsplit == 1 runs the prefill kernel. */
+int B200LmOps_Attention(int32_t device, const float* q, const float* k, const float* v, int32_t t, int32_t s,
+                        int32_t hq, int32_t hkv, int32_t hd, int32_t qpos0, int32_t window,
+                        int32_t kv_bf16, int32_t nsplit, int32_t repeat, float* out, float* ms_out,
+                        char** err);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200LM_OPS_H_ */

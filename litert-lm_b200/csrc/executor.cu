@@ -1,0 +1,824 @@
+// The B200 executor: model upload, paged KV cache, the reference's executor
+// state machine (token hold-back, step counter, bucketed work groups) and the
+// kernel orchestration for prefill and decode, behind the C ABI of b200lm.h.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <stdio.h>
+#include <stdlib.h>
+
+#include <algorithm>
+#include <fstream>
+#include <memory>
+#include <string>
+#include <vector>
+
+#include "../../include/b200lm.h"
+#include "common.cuh"
+#include "decode_ops.cuh"
+#include "model_host.h"
+#include "prefill_ops.cuh"
+#include "runtime.h"
+
+namespace b200lm {
+
+// ------------------------------------------------------------------ the model
+
+Model::~Model() {
+  cudaSetDevice(device);
+  for (void* p : allocations) cudaFree(p);
+}
+
+void* Model::alloc(size_t bytes) {
+  void* p = nullptr;
+  B2_CUDA(cudaMalloc(&p, std::max<size_t>(bytes, 256)));
+  allocations.push_back(p);
+  return p;
+}
+
+template <typename T>
+static T* upload(Model& m, const T* host, size_t count) {
+  T* d = reinterpret_cast<T*>(m.alloc(count * sizeof(T)));
+  B2_CUDA(cudaMemcpy(d, host, count * sizeof(T), cudaMemcpyHostToDevice));
+  return d;
+}
+
+static const uint4* upload_w4t(Model& m, const uint8_t* packed, int64_t rows, int64_t K) {
+  std::vector<uint32_t> buf((size_t)rows * K / 8);
+  repack_w4t(packed, rows, K, [](int64_t r) { return r; }, buf.data());
+  return reinterpret_cast<const uint4*>(upload(m, buf.data(), buf.size()));
+}
+
+// W4G with rows padded to 128; scales padded with 1.0.
+static void upload_w4g(Model& m, const uint8_t* packed, const float* scale, int64_t rows, int64_t K,
+                       const uint8_t** w_out, const float** s_out) {
+  int64_t tiles = (rows + 127) / 128;
+  std::vector<uint32_t> buf((size_t)tiles * 128 * K / 8);
+  repack_w4g(packed, tiles, K, [rows](int64_t r) { return r < rows ? r : (int64_t)-1; }, buf.data());
+  std::vector<float> sc((size_t)tiles * 128, 1.0f);
+  std::copy(scale, scale + rows, sc.begin());
+  *w_out = reinterpret_cast<const uint8_t*>(upload(m, buf.data(), buf.size()));
+  *s_out = upload(m, sc.data(), sc.size());
+}
+
+std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, bool want_tc) {
+  WeightsRecord rec = locate_weights(image, n);
+  auto m = std::make_shared<Model>();
+  m->device = device;
+  m->dims = rec.dims;
+  const ModelDims& d = m->dims;
+  B2_CUDA(cudaSetDevice(device));
+  auto bytes = [&](const TensorEntry& e) { return rec.base + e.offset; };
+  auto fvec = [&](const std::string& nm, size_t count) {
+    const TensorEntry& e = rec.need(nm, 1);
+    B2_CHECK(e.nbytes == count * 4, kInvalidArgument, "tensor has the wrong size: " + nm);
+    return upload(*m, reinterpret_cast<const float*>(bytes(e)), count);
+  };
+  auto qmat = [&](const std::string& nm, int64_t rows, int64_t K) -> const TensorEntry& {
+    const TensorEntry& e = rec.need(nm + ".q", 0);
+    B2_CHECK((int64_t)e.rows == rows && (int64_t)e.cols == K && (int64_t)e.nbytes == rows * K / 2,
+             kInvalidArgument, "matrix has the wrong shape: " + nm);
+    return e;
+  };
+  // tied embedding: canonical rows for the gather, mma tiles for the head
+  {
+    const TensorEntry& e = qmat("embed", d.vocab, d.d);
+    m->embed_rows = upload(*m, bytes(e), (size_t)e.nbytes);
+    m->embed_scale = fvec("embed.scale", d.vocab);
+    m->head_w = upload_w4t(*m, bytes(e), d.vocab, d.d);
+  }
+  m->g_final = fvec("final_norm", d.d);
+  m->layers_host.resize(d.n_layers);
+  m->gemm_host.resize(d.n_layers);
+  for (int i = 0; i < d.n_layers; ++i) {
+    std::string p = "L" + std::to_string(i) + ".";
+    LayerWeights& L = m->layers_host[i];
+    LayerGemmWeights& Gm = m->gemm_host[i];
+    memset(&L, 0, sizeof L);
+    memset(&Gm, 0, sizeof Gm);
+    const TensorEntry& eqkv = qmat(p + "wqkv", d.nqkv(), d.d);
+    const TensorEntry& eo = qmat(p + "wo", d.d, d.nq());
+    const TensorEntry& eg = qmat(p + "wgate", d.ffn, d.d);
+    const TensorEntry& eu = qmat(p + "wup", d.ffn, d.d);
+    const TensorEntry& ed = qmat(p + "wdown", d.d, d.ffn);
+    const float* sqkv = reinterpret_cast<const float*>(bytes(rec.need(p + "wqkv.scale", 1)));
+    const float* so = reinterpret_cast<const float*>(bytes(rec.need(p + "wo.scale", 1)));
+    const float* sg = reinterpret_cast<const float*>(bytes(rec.need(p + "wgate.scale", 1)));
+    const float* su = reinterpret_cast<const float*>(bytes(rec.need(p + "wup.scale", 1)));
+    const float* sd = reinterpret_cast<const float*>(bytes(rec.need(p + "wdown.scale", 1)));
+    L.wqkv = upload_w4t(*m, bytes(eqkv), d.nqkv(), d.d);
+    L.sqkv = upload(*m, sqkv, d.nqkv());
+    L.wo = upload_w4t(*m, bytes(eo), d.d, d.nq());
+    L.so = upload(*m, so, d.d);
+    L.wdown = upload_w4t(*m, bytes(ed), d.d, d.ffn);
+    L.sdown = upload(*m, sd, d.d);
+    // gate and up share one matrix: canonical rows [gate ; up]
+    std::vector<uint8_t> gu((size_t)2 * d.ffn * d.d / 2);
+    memcpy(gu.data(), bytes(eg), (size_t)eg.nbytes);
+    memcpy(gu.data() + eg.nbytes, bytes(eu), (size_t)eu.nbytes);
+    const int64_t ffn = d.ffn;
+    {   // decode layout: 16-row tiles alternate gate, up
+      std::vector<uint32_t> buf((size_t)2 * ffn * d.d / 8);
+      auto map = [ffn](int64_t r) {
+        int64_t tile = r / 16, pair = tile / 2;
+        return (tile & 1 ? ffn : (int64_t)0) + pair * 16 + (r % 16);
+      };
+      repack_w4t(gu.data(), 2 * ffn, d.d, map, buf.data());
+      L.wgu = reinterpret_cast<const uint4*>(upload(*m, buf.data(), buf.size()));
+      std::vector<float> sc((size_t)2 * ffn);
+      for (int64_t r = 0; r < 2 * ffn; ++r) {
+        int64_t src = map(r);
+        sc[r] = src < ffn ? sg[src] : su[src - ffn];
+      }
+      L.sgu = upload(*m, sc.data(), sc.size());
+    }
+    L.g_pre_attn = fvec(p + "pre_attn", d.d);
+    L.g_post_attn = fvec(p + "post_attn", d.d);
+    L.g_pre_ffn = fvec(p + "pre_ffn", d.d);
+    L.g_post_ffn = fvec(p + "post_ffn", d.d);
+    L.g_q = fvec(p + "q_norm", d.hd);
+    L.g_k = fvec(p + "k_norm", d.hd);
+    L.is_global = d.is_global(i) ? 1 : 0;
+    if (want_tc) {
+      upload_w4g(*m, bytes(eqkv), sqkv, d.nqkv(), d.d, &Gm.wqkv, &Gm.sqkv);
+      upload_w4g(*m, bytes(eo), so, d.d, d.nq(), &Gm.wo, &Gm.so);
+      upload_w4g(*m, bytes(ed), sd, d.d, d.ffn, &Gm.wdown, &Gm.sdown);
+      // 128-row tiles: 64 gate rows then the matching 64 up rows
+      int64_t tiles = ffn / 64;
+      std::vector<uint32_t> buf((size_t)tiles * 128 * d.d / 8);
+      auto map = [ffn](int64_t r) {
+        int64_t j = r / 128, c = r % 128;
+        return c < 64 ? j * 64 + c : ffn + j * 64 + (c - 64);
+      };
+      repack_w4g(gu.data(), tiles, d.d, map, buf.data());
+      Gm.wgu = reinterpret_cast<const uint8_t*>(upload(*m, buf.data(), buf.size()));
+      std::vector<float> sc((size_t)tiles * 128);
+      for (int64_t r = 0; r < tiles * 128; ++r) {
+        int64_t src = map(r);
+        sc[r] = src < ffn ? sg[src] : su[src - ffn];
+      }
+      Gm.sgu = upload(*m, sc.data(), sc.size());
+    }
+  }
+  m->has_tc = want_tc;
+  m->layers_dev = upload(*m, m->layers_host.data(), m->layers_host.size());
+  for (int t = 0; t < 2; ++t) {
+    std::vector<float> c, s;
+    build_rope_table(t ? d.rope_global : d.rope_local, d.hd, d.max_ctx, c, s);
+    m->rope_cos[t] = upload(*m, c.data(), c.size());
+    m->rope_sin[t] = upload(*m, s.data(), s.size());
+  }
+  return m;
+}
+
+// --------------------------------------------------------------- tensor maps
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    B2_CUDA(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q));
+    B2_CHECK(p != nullptr && q == cudaDriverEntryPointSuccess, kInternal, "cuTensorMapEncodeTiled unavailable");
+    fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// bf16 row-major [rows][cols]; box = 64 columns x 128 rows, 128-byte swizzle.
+CUtensorMap make_activation_map(const __nv_bfloat16* base, int rows, int cols) {
+  CUtensorMap tm;
+  cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)kGemmBM};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = encode_tiled_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(base), dims,
+                                 strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B2_CHECK(r == CUDA_SUCCESS, kInternal, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
+  return tm;
+}
+
+int pick_ksplit(int tiles, int KB, int sms) {
+  int best = 1;
+  for (int s = 1; s <= 8; ++s) {
+    if (KB % s) continue;
+    if (KB / s < 4) break;
+    best = s;
+    if (tiles * s >= 2 * sms) break;
+  }
+  return best;
+}
+
+// Launches one int4 GEMM.  a_map must describe `A` ([rows >= T][K] bf16).
+void launch_gemm(cudaStream_t st, int mode, const CUtensorMap& a_map, const __nv_bfloat16* A,
+                 const uint4* w4t, const float* s4t, const uint8_t* w4g, const float* s4g, int T, int N, int K,
+                 int ksplit, bool geglu, float* outF, __nv_bfloat16* outB, int* err, int64_t* launches) {
+  if (mode == B200LM_GEMM_TCGEN05) {
+    GemmArgs g{w4g, s4g, T, N, K, ksplit, outF, outB, err};
+    dim3 grid((N + kGemmBN - 1) / kGemmBN, (T + kGemmBM - 1) / kGemmBM, ksplit);
+    if (geglu) {
+      B2_CUDA(cudaFuncSetAttribute(gemm_w4_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+      gemm_w4_tc_kernel<1><<<grid, kGemmThreads, kGemmSmem, st>>>(a_map, g);
+    } else {
+      B2_CUDA(cudaFuncSetAttribute(gemm_w4_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
+      gemm_w4_tc_kernel<0><<<grid, kGemmThreads, kGemmSmem, st>>>(a_map, g);
+    }
+  } else {
+    B2_CHECK(ksplit == 1, kInternal, "the check GEMM does not split K");
+    dim3 grid(geglu ? N / 32 : N / 16, (T + 7) / 8);
+    gemm_w4_simple_kernel<<<grid, 128, 0, st>>>(A, w4t, s4t, T, N, K, geglu ? 1 : 0, outF, outB);
+  }
+  B2_CUDA(cudaGetLastError());
+  if (launches) ++*launches;
+}
+
+// --------------------------------------------------------------- the executor
+
+static int round_up(int v, int a) { return (v + a - 1) / a * a; }
+
+Executor::~Executor() {
+  cudaSetDevice(device);
+  if (stream) cudaStreamSynchronize(stream);
+  if (graph_exec) cudaGraphExecDestroy(graph_exec);
+  for (void* p : allocations) cudaFree(p);
+  if (pinned) cudaFreeHost(pinned);
+  if (own_stream && stream) cudaStreamDestroy(stream);
+}
+
+void* Executor::alloc(size_t bytes, bool zero) {
+  void* p = nullptr;
+  B2_CUDA(cudaMalloc(&p, std::max<size_t>(bytes, 256)));
+  allocations.push_back(p);
+  if (zero) B2_CUDA(cudaMemset(p, 0, std::max<size_t>(bytes, 256)));
+  return p;
+}
+
+std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B200LmConfig& cfg) {
+  auto e = std::unique_ptr<Executor>(new Executor());
+  e->model = model;
+  e->device = model->device;
+  const ModelDims& d = model->dims;
+  B2_CUDA(cudaSetDevice(e->device));
+  cudaDeviceProp prop;
+  B2_CUDA(cudaGetDeviceProperties(&prop, e->device));
+  B2_CHECK(prop.major == 10, kFailedPrecondition,
+           "this library is built for sm_100a (B200); device reports sm_" + std::to_string(prop.major) +
+               std::to_string(prop.minor));
+  e->n_sms = prop.multiProcessorCount;
+  if (cfg.stream) {
+    e->stream = reinterpret_cast<cudaStream_t>(cfg.stream);
+  } else {
+    B2_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
+    e->own_stream = true;
+  }
+  e->max_num_tokens = cfg.max_num_tokens > 0 ? std::min(cfg.max_num_tokens, d.max_ctx) : d.max_ctx;
+  e->prefill_gemm = cfg.prefill_gemm == B200LM_GEMM_AUTO ? (model->has_tc ? B200LM_GEMM_TCGEN05 : B200LM_GEMM_CHECK)
+                                                          : cfg.prefill_gemm;
+  B2_CHECK(e->prefill_gemm != B200LM_GEMM_TCGEN05 || model->has_tc, kFailedPrecondition,
+           "tensor-core GEMM weights were not loaded for this model");
+  e->decode_mode = cfg.decode_mode == B200LM_DECODE_AUTO ? B200LM_DECODE_PERSISTENT : cfg.decode_mode;
+  const int esz = d.kv_dtype == 0 ? 4 : 2;
+  // ---- paged KV cache
+  e->pages_per_seq = (d.max_ctx + kPage - 1) / kPage;
+  size_t pool = (size_t)e->pages_per_seq * d.hkv * kPage * d.hd;
+  e->kv_host.resize(d.n_layers);
+  for (int i = 0; i < d.n_layers; ++i) {
+    e->kv_host[i].k = e->alloc(pool * esz, true);
+    e->kv_host[i].v = e->alloc(pool * esz, true);
+    e->kv_host[i].k16 = nullptr;
+    e->kv_host[i].v16 = nullptr;
+  }
+  LayerKv* kvd = reinterpret_cast<LayerKv*>(e->alloc(sizeof(LayerKv) * d.n_layers, false));
+  B2_CUDA(cudaMemcpy(kvd, e->kv_host.data(), sizeof(LayerKv) * d.n_layers, cudaMemcpyHostToDevice));
+  e->kv_dev = kvd;
+  e->page_table_host.resize(e->pages_per_seq);
+  for (int i = 0; i < e->pages_per_seq; ++i)
+    e->page_table_host[i] = (cfg.reserved0 & 1) ? e->pages_per_seq - 1 - i : i;   // bit 0: reversed page order
+  int* ptd = reinterpret_cast<int*>(e->alloc(sizeof(int) * e->pages_per_seq, false));
+  B2_CUDA(cudaMemcpy(ptd, e->page_table_host.data(), sizeof(int) * e->pages_per_seq, cudaMemcpyHostToDevice));
+  e->page_table_dev = ptd;
+  // ---- decode buffers
+  DecodeArgs& a = e->dargs;
+  memset(&a, 0, sizeof a);
+  a.dims = d;
+  a.ncols = 1;
+  a.nterms = 3;
+  a.n_attn_splits_local = std::max(1, std::min(32, d.window / 64));
+  a.n_attn_splits_global = std::max(1, std::min(32, d.max_ctx / 128));
+  int hps = 1;
+  while ((hps * d.hd) % 64 != 0) ++hps;
+  B2_CHECK(d.hq % hps == 0, kUnimplemented, "q heads cannot be grouped into 64-wide slices");
+  a.o_slices = d.hq / hps;
+  while (a.o_slices > e->n_sms) a.o_slices /= 2;
+  int KTd = d.ffn / 64;
+  a.down_slices = 1;
+  for (int s = 4; s >= 2; --s)
+    if (KTd % s == 0 && (d.d / 16) * s <= e->n_sms) { a.down_slices = s; break; }
+  a.layers = model->layers_dev;
+  a.kv = e->kv_dev;
+  a.page_table = e->page_table_dev;
+  a.pages_per_seq = e->pages_per_seq;
+  a.embed_rows = model->embed_rows;
+  a.embed_scale = model->embed_scale;
+  a.head_w = model->head_w;
+  a.g_final = model->g_final;
+  for (int t = 0; t < 2; ++t) { a.rope_cos[t] = model->rope_cos[t]; a.rope_sin[t] = model->rope_sin[t]; }
+  a.st = reinterpret_cast<DecodeState*>(e->alloc(sizeof(DecodeState), true));
+  const int G = d.group();
+  const int max_splits = std::max(a.n_attn_splits_local, a.n_attn_splits_global);
+  a.xres[0] = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.d, true));
+  a.xres[1] = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.d, true));
+  a.qkv = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.nqkv(), true));
+  a.part_o = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.hkv * max_splits * G * d.hd, true));
+  a.part_ml = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.hkv * max_splits * G * 2, true));
+  a.opart = reinterpret_cast<float*>(e->alloc(sizeof(float) * a.o_slices * kMaxCols * d.d, true));
+  a.act = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.ffn, true));
+  a.fpart = reinterpret_cast<float*>(e->alloc(sizeof(float) * a.down_slices * kMaxCols * d.d, true));
+  a.logits = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.vocab, true));
+  a.amax_val = reinterpret_cast<float*>(e->alloc(sizeof(float) * e->n_sms * kMaxCols, true));
+  a.amax_idx = reinterpret_cast<int*>(e->alloc(sizeof(int) * e->n_sms * kMaxCols, true));
+  a.step_capacity = d.max_ctx;
+  a.step_tokens = reinterpret_cast<int*>(e->alloc(sizeof(int) * a.step_capacity * kMaxCols, true));
+  a.advance = 1;
+  e->dec_smem = dec_smem_bytes(d, a.ncols);
+  B2_CHECK(e->dec_smem <= (size_t)prop.sharedMemPerBlockOptin, kUnimplemented,
+           "decode kernels need more shared memory than the device offers");
+  B2_CUDA(cudaFuncSetAttribute(decode_phase_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->dec_smem));
+  B2_CUDA(cudaFuncSetAttribute(decode_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->dec_smem));
+  if (e->decode_mode == B200LM_DECODE_PERSISTENT) {
+    int occ = 0;
+    B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_persistent_kernel, kDecThreads, e->dec_smem));
+    if (occ < 1 || !prop.cooperativeLaunch) e->decode_mode = B200LM_DECODE_PHASE_KERNELS;
+  }
+  // ---- prefill buffers (rows padded to whole 128-token tiles, zero-filled)
+  e->t_max = d.buckets[0];
+  e->t_pad = round_up(e->t_max, kGemmBM);
+  const size_t tp = e->t_pad;
+  e->pf_tokens = reinterpret_cast<int*>(e->alloc(sizeof(int) * tp, true));
+  e->pf_xres = reinterpret_cast<float*>(e->alloc(sizeof(float) * tp * d.d, true));
+  e->pf_h = reinterpret_cast<__nv_bfloat16*>(e->alloc(2 * tp * d.d, true));
+  e->pf_qkv = reinterpret_cast<float*>(e->alloc(sizeof(float) * tp * d.nqkv(), true));
+  e->pf_attn = reinterpret_cast<__nv_bfloat16*>(e->alloc(2 * tp * d.nq(), true));
+  e->pf_act = reinterpret_cast<__nv_bfloat16*>(e->alloc(2 * tp * d.ffn, true));
+  e->pf_parts = reinterpret_cast<float*>(e->alloc(sizeof(float) * 8 * tp * d.d, true));
+  if (e->prefill_gemm == B200LM_GEMM_TCGEN05) {
+    e->tm_h = make_activation_map(e->pf_h, (int)tp, d.d);
+    e->tm_attn = make_activation_map(e->pf_attn, (int)tp, d.nq());
+    e->tm_act = make_activation_map(e->pf_act, (int)tp, d.ffn);
+  }
+  size_t pin = sizeof(float) * (size_t)d.vocab + sizeof(int) * (tp + (size_t)d.max_ctx * kMaxCols) + 4096;
+  B2_CUDA(cudaMallocHost(&e->pinned, pin));
+  e->pin_logits = reinterpret_cast<float*>(e->pinned);
+  e->pin_ints = reinterpret_cast<int*>(e->pin_logits + d.vocab);
+  e->pin_state = reinterpret_cast<DecodeState*>(e->pin_ints + tp + (size_t)d.max_ctx * kMaxCols);
+  B2_CUDA(cudaDeviceSynchronize());
+  return e;
+}
+
+void Executor::check_device_error(const char* where) {
+  int err = 0;
+  B2_CUDA(cudaMemcpyAsync(&pin_state->err, &dargs.st->err, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  B2_CUDA(cudaStreamSynchronize(stream));
+  err = pin_state->err;
+  if (err == kDevOk) return;
+  // clear the word and the barrier count so the handle stays usable
+  B2_CUDA(cudaMemsetAsync(&dargs.st->err, 0, sizeof(int), stream));
+  B2_CUDA(cudaMemsetAsync(&dargs.st->barrier, 0, sizeof(unsigned), stream));
+  B2_CUDA(cudaStreamSynchronize(stream));
+  barrier_epoch = 0;
+  std::string w(where);
+  if (err == kDevBarrierTimeout) throw Error{kDeadlineExceeded, w + ": a bounded device-side wait gave up"};
+  if (err == kDevBadToken) throw Error{kInvalidArgument, w + ": token id outside the vocabulary"};
+  if (err == kDevBadPosition) throw Error{kInvalidArgument, w + ": position outside the KV capacity"};
+  throw Error{kInternal, w + ": device error word " + std::to_string(err)};
+}
+
+// ------------------------------------------------------------------- prefill
+
+template <typename T>
+static void launch_kv_append(cudaStream_t st, const ModelDims& d, int T_, const float* qkv, int pos0, const int* pt,
+                             const LayerWeights& L, const float* c, const float* s, const LayerKv& kv) {
+  pf_kv_append_kernel<T><<<T_, kPfThreads, 0, st>>>(d, qkv, pos0, pt, L.g_k, c, s, kv);
+}
+
+void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
+  const ModelDims& d = model->dims;
+  B2_CHECK(T <= t_max, kInternal, "prefill chunk larger than the largest bucket");
+  B2_CHECK(start + T <= max_num_tokens, kInvalidArgument,
+           "Input token ids are too long. Exceeding the maximum number of tokens allowed: " +
+               std::to_string(start + T) + " > " + std::to_string(max_num_tokens));
+  memcpy(pin_ints, tokens, sizeof(int) * T);
+  B2_CUDA(cudaMemcpyAsync(pf_tokens, pin_ints, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
+  h2d_bytes += sizeof(int) * (size_t)T;
+  int* err = &dargs.st->err;
+  const size_t sm_d = sizeof(float) * d.d;
+  pf_embed_norm_kernel<<<T, kPfThreads, sm_d, stream>>>(pf_tokens, model->embed_rows, model->embed_scale,
+                                                        model->layers_host[0].g_pre_attn, d.d, d.vocab, d.eps,
+                                                        pf_xres, pf_h, err);
+  ++launches;
+  const int mode = prefill_gemm;
+  const int mt = (T + kGemmBM - 1) / kGemmBM;
+  const size_t attn_smem = sizeof(float) * ((size_t)(d.group() + 2) * d.hd + (size_t)8 * d.group() * (d.hd + 2));
+  B2_CUDA(cudaFuncSetAttribute(pf_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem));
+  for (int li = 0; li < d.n_layers; ++li) {
+    const LayerWeights& L = model->layers_host[li];
+    const LayerGemmWeights& Gm = model->gemm_host[li];
+    const float* cosT = model->rope_cos[L.is_global];
+    const float* sinT = model->rope_sin[L.is_global];
+    launch_gemm(stream, mode, tm_h, pf_h, L.wqkv, L.sqkv, Gm.wqkv, Gm.sqkv, T, d.nqkv(), d.d, 1, false, pf_qkv,
+                nullptr, err, &launches);
+    if (d.kv_dtype == 0) launch_kv_append<float>(stream, d, T, pf_qkv, start, page_table_dev, L, cosT, sinT, kv_host[li]);
+    else launch_kv_append<__nv_bfloat16>(stream, d, T, pf_qkv, start, page_table_dev, L, cosT, sinT, kv_host[li]);
+    ++launches;
+    AttnJob j;
+    memset(&j, 0, sizeof j);
+    j.qkv = pf_qkv;
+    j.pos = nullptr;
+    j.pos0 = start;
+    j.page_table = page_table_dev;
+    j.pages_per_seq = pages_per_seq;
+    j.seq_stride = 0;
+    j.is_global = L.is_global;
+    j.nsplit = 1;
+    j.appended = 1;
+    j.g_q = L.g_q;
+    j.g_k = L.g_k;
+    j.cosT = cosT;
+    j.sinT = sinT;
+    j.kv = kv_host[li];
+    j.out_bf16 = pf_attn;
+    j.err = err;
+    pf_attn_kernel<<<T * d.hkv, 256, attn_smem, stream>>>(d, j);
+    ++launches;
+    int ks_o = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(mt * ((d.d + kGemmBN - 1) / kGemmBN), d.nq() / 64, n_sms) : 1;
+    launch_gemm(stream, mode, tm_attn, pf_attn, L.wo, L.so, Gm.wo, Gm.so, T, d.d, d.nq(), ks_o, false, pf_parts,
+                nullptr, err, &launches);
+    pf_resid_norm_kernel<<<T, kPfThreads, sm_d, stream>>>(pf_parts, ks_o, (size_t)T * d.d, d.d, d.eps, L.g_post_attn,
+                                                          L.g_pre_ffn, pf_xres, pf_h);
+    ++launches;
+    launch_gemm(stream, mode, tm_h, pf_h, L.wgu, L.sgu, Gm.wgu, Gm.sgu, T, 2 * d.ffn, d.d, 1, true, nullptr, pf_act,
+                err, &launches);
+    int ks_d = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(mt * ((d.d + kGemmBN - 1) / kGemmBN), d.ffn / 64, n_sms) : 1;
+    launch_gemm(stream, mode, tm_act, pf_act, L.wdown, L.sdown, Gm.wdown, Gm.sdown, T, d.d, d.ffn, ks_d, false,
+                pf_parts, nullptr, err, &launches);
+    const float* g_next = li + 1 < d.n_layers ? model->layers_host[li + 1].g_pre_attn : nullptr;
+    pf_resid_norm_kernel<<<T, kPfThreads, sm_d, stream>>>(pf_parts, ks_d, (size_t)T * d.d, d.d, d.eps, L.g_post_ffn,
+                                                          g_next, pf_xres, pf_h);
+    ++launches;
+  }
+  B2_CUDA(cudaGetLastError());
+}
+
+// llm_litert_compiled_model_executor.cc:157-276: a group of `len` ids runs the
+// pending id (if any) followed by ids[0..len-2]; ids[len-1] becomes pending.
+void Executor::prefill_group(const int* ids, int len) {
+  std::vector<int> run;
+  run.reserve(len);
+  int start = current_step;
+  for (int i = 0; i < len - 1;) {
+    if (next_input_token != -1) {
+      run.push_back(next_input_token);
+      next_input_token = -1;
+    } else {
+      run.push_back(ids[i++]);
+    }
+    ++current_step;
+  }
+  next_input_token = ids[len - 1];
+  if (!run.empty()) {
+    try {
+      run_prefill_chunk(run.data(), (int)run.size(), start);
+    } catch (...) {
+      throw;
+    }
+  }
+}
+
+void Executor::prefill(const int* ids, int n, bool wait, const volatile int* cancel) {
+  B2_CHECK(ids != nullptr, kInvalidArgument, "ids is null");
+  B2_CHECK(n > 0, kInternal, "Prefill token ids must be non-empty.");
+  B2_CUDA(cudaSetDevice(device));
+  const ModelDims& d = model->dims;
+  auto groups = plan_work_groups(d.buckets, d.n_buckets, n);
+  last_plan = groups;
+  int used = 0;
+  for (auto& g : groups) {
+    if (cancel && *cancel) throw Error{kCancelled, "Prefill cancelled."};
+    prefill_group(ids + used, g.second);
+    used += g.second;
+  }
+  B2_CHECK(used == n, kInternal, "Work groups not covering the entire prefill input.");
+  if (wait) check_device_error("Prefill");
+}
+
+// -------------------------------------------------------------------- decode
+
+void Executor::launch_decode_steps(int nsteps) {
+  const ModelDims& d = model->dims;
+  const int ncta = n_sms;
+  if (decode_mode == B200LM_DECODE_PERSISTENT) {
+    DecodeArgs a = dargs;
+    unsigned epoch0 = barrier_epoch;
+    void* params[] = {&a, &nsteps, &epoch0};
+    B2_CUDA(cudaLaunchCooperativeKernel((void*)decode_persistent_kernel, dim3(ncta), dim3(kDecThreads), params,
+                                        dec_smem, stream));
+    barrier_epoch += (unsigned)nsteps * (unsigned)(5 * d.n_layers + 2) * (unsigned)ncta;
+    launches += 1;
+    return;
+  }
+  if (!graph_exec) {
+    cudaGraph_t graph;
+    B2_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    for (int li = 0; li < d.n_layers; ++li)
+      for (int ph = kPhQkv; ph <= kPhDown; ++ph)
+        decode_phase_kernel<<<ncta, kDecThreads, dec_smem, stream>>>(dargs, ph, li);
+    decode_phase_kernel<<<ncta, kDecThreads, dec_smem, stream>>>(dargs, kPhHead, 0);
+    decode_phase_kernel<<<1, kDecThreads, dec_smem, stream>>>(dargs, kPhArgmax, ncta);
+    B2_CUDA(cudaStreamEndCapture(stream, &graph));
+    B2_CUDA(cudaGraphInstantiate(&graph_exec, graph, 0));
+    cudaGraphDestroy(graph);
+  }
+  for (int s = 0; s < nsteps; ++s) B2_CUDA(cudaGraphLaunch(graph_exec, stream));
+  launches += (int64_t)nsteps * (5 * d.n_layers + 2);
+}
+
+void Executor::push_decode_state(int token, int pos) {
+  DecodeState* ps = pin_state;
+  memset(ps, 0, sizeof(DecodeState));
+  ps->token[0] = token;
+  ps->pos[0] = pos;
+  // token, pos, out_token: the first three arrays; err / barrier / steps_done handled separately
+  B2_CUDA(cudaMemcpyAsync(dargs.st, ps, offsetof(DecodeState, err), cudaMemcpyHostToDevice, stream));
+  B2_CUDA(cudaMemsetAsync(&dargs.st->steps_done, 0, sizeof(int), stream));
+  h2d_bytes += 2 * sizeof(int);
+}
+
+int Executor::take_decode_id(const int* id_or_null) {
+  int id = next_input_token;
+  if (id_or_null) id = *id_or_null;
+  B2_CHECK(id != -1, kInvalidArgument, "No id available to be decoded.");
+  next_input_token = -1;
+  B2_CHECK(current_step < max_num_tokens, kInvalidArgument, "Maximum kv-cache size reached.");
+  return id;
+}
+
+void Executor::decode_logits(const int* id_or_null, float* host_logits) {
+  B2_CHECK(host_logits != nullptr, kInvalidArgument, "logits destination is null");
+  B2_CUDA(cudaSetDevice(device));
+  int id = take_decode_id(id_or_null);
+  push_decode_state(id, current_step);
+  launch_decode_steps(1);
+  const size_t nb = sizeof(float) * (size_t)model->dims.vocab;
+  B2_CUDA(cudaMemcpyAsync(pin_logits, dargs.logits, nb, cudaMemcpyDeviceToHost, stream));
+  d2h_bytes += nb;
+  check_device_error("DecodeLogits");
+  memcpy(host_logits, pin_logits, nb);
+  ++current_step;
+}
+
+void Executor::decode_tokens(int nsteps, int* out_ids) {
+  B2_CHECK(nsteps > 0, kInvalidArgument, "n_steps must be positive");
+  B2_CUDA(cudaSetDevice(device));
+  B2_CHECK(current_step + nsteps <= max_num_tokens, kInvalidArgument, "Maximum kv-cache size reached.");
+  int id = take_decode_id(nullptr);
+  push_decode_state(id, current_step);
+  launch_decode_steps(nsteps);
+  int* dst = pin_ints + t_pad;
+  B2_CUDA(cudaMemcpyAsync(dst, dargs.step_tokens, sizeof(int) * (size_t)nsteps * dargs.ncols, cudaMemcpyDeviceToHost,
+                          stream));
+  d2h_bytes += sizeof(int) * (size_t)nsteps;
+  check_device_error("Decode");
+  for (int s = 0; s < nsteps; ++s) {
+    int t = dst[(size_t)s * dargs.ncols];
+    if (t < 0) t = 0;   // "The sampled token is casted to 0 to avoid crash."
+    if (out_ids) out_ids[s] = t;
+    next_input_token = t;
+  }
+  current_step += nsteps;
+}
+
+void Executor::reset() {
+  current_step = 0;
+  next_input_token = -1;
+}
+
+void Executor::read_kv_row(int layer, int is_v, int kv_head, int pos, float* out, int* page, int* slot) {
+  const ModelDims& d = model->dims;
+  B2_CHECK(layer >= 0 && layer < d.n_layers && kv_head >= 0 && kv_head < d.hkv && pos >= 0 && pos < d.max_ctx,
+           kInvalidArgument, "KV row index out of range");
+  B2_CUDA(cudaSetDevice(device));
+  B2_CUDA(cudaStreamSynchronize(stream));
+  int pg = page_table_host[pos / kPage], sl = pos % kPage;
+  size_t off = (((size_t)pg * d.hkv + kv_head) * kPage + sl) * d.hd;
+  const void* base = is_v ? kv_host[layer].v : kv_host[layer].k;
+  if (d.kv_dtype == 0) {
+    B2_CUDA(cudaMemcpy(out, reinterpret_cast<const float*>(base) + off, sizeof(float) * d.hd, cudaMemcpyDeviceToHost));
+  } else {
+    std::vector<__nv_bfloat16> tmp(d.hd);
+    B2_CUDA(cudaMemcpy(tmp.data(), reinterpret_cast<const __nv_bfloat16*>(base) + off, 2 * d.hd, cudaMemcpyDeviceToHost));
+    for (int i = 0; i < d.hd; ++i) out[i] = __bfloat162float(tmp[i]);
+  }
+  if (page) *page = pg;
+  if (slot) *slot = sl;
+}
+
+}  // namespace b200lm
+
+// ===================================================================== C ABI
+
+using namespace b200lm;
+
+struct B200LmExecutor {
+  std::unique_ptr<Executor> impl;
+};
+
+static int fail(char** err, int code, const std::string& msg) {
+  if (err) {
+    *err = reinterpret_cast<char*>(malloc(msg.size() + 1));
+    if (*err) memcpy(*err, msg.c_str(), msg.size() + 1);
+  }
+  return code;
+}
+
+#define B2_API_BEGIN \
+  if (err) *err = nullptr; \
+  try {
+#define B2_API_END                                                     \
+  }                                                                    \
+  catch (const Error& e_) { return fail(err, e_.code, e_.msg); }       \
+  catch (const std::exception& e_) { return fail(err, kInternal, e_.what()); } \
+  catch (...) { return fail(err, kInternal, "unknown failure"); }      \
+  return kOk;
+
+static void require_gpu(int device) {
+  int n = 0;
+  cudaError_t r = cudaGetDeviceCount(&n);
+  if (r != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    throw Error{kFailedPrecondition, "no CUDA device: this backend has no CPU fallback"};
+  }
+  B2_CHECK(device >= 0 && device < n, kInvalidArgument, "device ordinal out of range");
+}
+
+static B200LmConfig effective_config(const B200LmConfig* c) {
+  B200LmConfig cfg;
+  memset(&cfg, 0, sizeof cfg);
+  if (c) memcpy(&cfg, c, std::min<size_t>(sizeof cfg, c->struct_size > 0 ? (size_t)c->struct_size : sizeof cfg));
+  return cfg;
+}
+
+extern "C" {
+
+int B200Lm_Create(const B200LmConfig* config, const void* bytes, uint64_t n_bytes, const char* path,
+                  B200LmExecutor** out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(out != nullptr, kInvalidArgument, "out is null");
+  *out = nullptr;
+  B200LmConfig cfg = effective_config(config);
+  std::vector<uint8_t> file;
+  const uint8_t* p = reinterpret_cast<const uint8_t*>(bytes);
+  if (!p) {
+    B2_CHECK(path != nullptr, kInvalidArgument, "neither bytes nor a path were given");
+    std::ifstream f(path, std::ios::binary | std::ios::ate);
+    B2_CHECK(f.good(), kNotFound, std::string("cannot open ") + path);
+    std::streamsize sz = f.tellg();
+    f.seekg(0);
+    file.resize((size_t)sz);
+    f.read(reinterpret_cast<char*>(file.data()), sz);
+    B2_CHECK(f.good(), kInternal, std::string("cannot read ") + path);
+    p = file.data();
+    n_bytes = (uint64_t)sz;
+  }
+  // Parse first: malformed input is reported as such even without a GPU.
+  (void)locate_weights(p, (size_t)n_bytes);
+  require_gpu(cfg.device);
+  auto model = Model::load(p, (size_t)n_bytes, cfg.device, cfg.prefill_gemm != B200LM_GEMM_CHECK);
+  auto h = new B200LmExecutor();
+  try {
+    h->impl = Executor::create(model, cfg);
+  } catch (...) {
+    delete h;
+    throw;
+  }
+  *out = h;
+  B2_API_END
+}
+
+int B200Lm_CreateShared(B200LmExecutor* owner, const B200LmConfig* config, B200LmExecutor** out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(owner && owner->impl && out, kInvalidArgument, "null handle");
+  B200LmConfig cfg = effective_config(config);
+  cfg.device = owner->impl->device;
+  auto h = new B200LmExecutor();
+  try {
+    h->impl = Executor::create(owner->impl->model, cfg);
+  } catch (...) {
+    delete h;
+    throw;
+  }
+  *out = h;
+  B2_API_END
+}
+
+void B200Lm_Destroy(B200LmExecutor* e) { delete e; }
+
+int B200Lm_Prefill(B200LmExecutor* e, const int32_t* ids, int32_t n, int32_t wait, const volatile int32_t* cancel,
+                   char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
+  e->impl->prefill(ids, n, wait != 0, cancel);
+  B2_API_END
+}
+
+int B200Lm_DecodeLogits(B200LmExecutor* e, const int32_t* id, float* logits, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
+  e->impl->decode_logits(id, logits);
+  B2_API_END
+}
+
+int B200Lm_DecodeToken(B200LmExecutor* e, int32_t* out_id, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out_id, kInvalidArgument, "null argument");
+  e->impl->decode_tokens(1, out_id);
+  B2_API_END
+}
+
+int B200Lm_DecodeTokens(B200LmExecutor* e, int32_t n_steps, int32_t* out_ids, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
+  e->impl->decode_tokens(n_steps, out_ids);
+  B2_API_END
+}
+
+int B200Lm_Reset(B200LmExecutor* e, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
+  e->impl->reset();
+  B2_API_END
+}
+
+int B200Lm_GetVocabSize(B200LmExecutor* e, int32_t* out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out, kInvalidArgument, "null argument");
+  *out = e->impl->model->dims.vocab;
+  B2_API_END
+}
+
+int B200Lm_GetCurrentStep(B200LmExecutor* e, int32_t* out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out, kInvalidArgument, "null argument");
+  *out = e->impl->current_step + (e->impl->next_input_token == -1 ? 0 : 1);
+  B2_API_END
+}
+
+int B200Lm_GetMaxNumTokens(B200LmExecutor* e, int32_t* out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out, kInvalidArgument, "null argument");
+  *out = e->impl->max_num_tokens;
+  B2_API_END
+}
+
+const char* B200Lm_BackendName(void) { return "B200 CUDA (sm_100a)"; }
+
+int B200Lm_Synchronize(B200LmExecutor* e, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
+  B2_CUDA(cudaSetDevice(e->impl->device));
+  e->impl->check_device_error("Synchronize");
+  B2_API_END
+}
+
+int B200Lm_GetLastPrefillPlan(B200LmExecutor* e, int32_t* buckets, int32_t* lengths, int32_t capacity,
+                              int32_t* n_groups, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && n_groups, kInvalidArgument, "null argument");
+  const auto& plan = e->impl->last_plan;
+  *n_groups = (int32_t)plan.size();
+  for (int i = 0; i < (int)plan.size() && i < capacity; ++i) {
+    if (buckets) buckets[i] = plan[i].first;
+    if (lengths) lengths[i] = plan[i].second;
+  }
+  B2_API_END
+}
+
+int B200Lm_ReadKvRow(B200LmExecutor* e, int32_t layer, int32_t is_v, int32_t kv_head, int32_t pos, float* out_row,
+                     int32_t* out_page, int32_t* out_slot, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out_row, kInvalidArgument, "null argument");
+  e->impl->read_kv_row(layer, is_v, kv_head, pos, out_row, out_page, out_slot);
+  B2_API_END
+}
+
+int B200Lm_GetLaunchCount(B200LmExecutor* e, int64_t* out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out, kInvalidArgument, "null argument");
+  *out = e->impl->launches;
+  B2_API_END
+}
+
+}  // extern "C"

@@ -1,0 +1,113 @@
+// Host-side classes of the B200 executor library.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <memory>
+#include <utility>
+#include <vector>
+
+#include "../../include/b200lm.h"
+#include "common.cuh"
+#include "decode_ops.cuh"
+
+namespace b200lm {
+
+// Tensor-core GEMM copies of the layer matrices (128-row x 64-k blocks).
+struct LayerGemmWeights {
+  const uint8_t *wqkv, *wo, *wgu, *wdown;
+  const float *sqkv, *so, *sgu, *sdown;
+};
+
+// Device-resident weights of one decoder; shared by every executor created
+// over it.
+struct Model {
+  int device = 0;
+  ModelDims dims{};
+  bool has_tc = false;
+  const uint8_t* embed_rows = nullptr;
+  const float* embed_scale = nullptr;
+  const uint4* head_w = nullptr;
+  const float* g_final = nullptr;
+  const float* rope_cos[2] = {nullptr, nullptr};
+  const float* rope_sin[2] = {nullptr, nullptr};
+  std::vector<LayerWeights> layers_host;
+  std::vector<LayerGemmWeights> gemm_host;
+  const LayerWeights* layers_dev = nullptr;
+  std::vector<void*> allocations;
+
+  ~Model();
+  void* alloc(size_t bytes);
+  static std::shared_ptr<Model> load(const uint8_t* image, size_t n, int device, bool want_tc);
+};
+
+CUtensorMap make_activation_map(const __nv_bfloat16* base, int rows, int cols);
+int pick_ksplit(int tiles, int KB, int sms);
+void launch_gemm(cudaStream_t st, int mode, const CUtensorMap& a_map, const __nv_bfloat16* A, const uint4* w4t,
+                 const float* s4t, const uint8_t* w4g, const float* s4g, int T, int N, int K, int ksplit, bool geglu,
+                 float* outF, __nv_bfloat16* outB, int* err, int64_t* launches);
+
+// One session: KV cache, step counter, pending token, scratch activations.
+class Executor {
+ public:
+  static std::unique_ptr<Executor> create(std::shared_ptr<Model> model, const B200LmConfig& cfg);
+  ~Executor();
+
+  void prefill(const int* ids, int n, bool wait, const volatile int* cancel);
+  void decode_logits(const int* id_or_null, float* host_logits);
+  void decode_tokens(int nsteps, int* out_ids);
+  void reset();
+  void check_device_error(const char* where);
+  void read_kv_row(int layer, int is_v, int kv_head, int pos, float* out, int* page, int* slot);
+
+  std::shared_ptr<Model> model;
+  int device = 0;
+  int n_sms = 0;
+  cudaStream_t stream = nullptr;
+  bool own_stream = false;
+  int max_num_tokens = 0;
+  int prefill_gemm = 0, decode_mode = 0;
+  // reference state machine (llm_litert_compiled_model_executor.h: current_step_, next_input_token_id_)
+  int current_step = 0;
+  int next_input_token = -1;
+  std::vector<std::pair<int, int>> last_plan;
+  int64_t launches = 0;
+  size_t h2d_bytes = 0, d2h_bytes = 0;
+
+ private:
+  Executor() = default;
+  void* alloc(size_t bytes, bool zero);
+  void run_prefill_chunk(const int* tokens, int T, int start);
+  void prefill_group(const int* ids, int len);
+  void launch_decode_steps(int nsteps);
+  void push_decode_state(int token, int pos);
+  int take_decode_id(const int* id_or_null);
+
+  std::vector<void*> allocations;
+  std::vector<LayerKv> kv_host;
+  const LayerKv* kv_dev = nullptr;
+  std::vector<int> page_table_host;
+  const int* page_table_dev = nullptr;
+  int pages_per_seq = 0;
+  DecodeArgs dargs{};
+  size_t dec_smem = 0;
+  unsigned barrier_epoch = 0;
+  cudaGraphExec_t graph_exec = nullptr;
+  // prefill scratch
+  int t_max = 0, t_pad = 0;
+  int* pf_tokens = nullptr;
+  float* pf_xres = nullptr;
+  __nv_bfloat16* pf_h = nullptr;
+  float* pf_qkv = nullptr;
+  __nv_bfloat16* pf_attn = nullptr;
+  __nv_bfloat16* pf_act = nullptr;
+  float* pf_parts = nullptr;
+  CUtensorMap tm_h{}, tm_attn{}, tm_act{};
+  // pinned staging
+  void* pinned = nullptr;
+  float* pin_logits = nullptr;
+  int* pin_ints = nullptr;
+  DecodeState* pin_state = nullptr;
+};
+
+}  // namespace b200lm
