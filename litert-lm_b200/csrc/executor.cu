@@ -503,6 +503,12 @@ void Executor::prefill(const int* ids, int n, bool wait, const volatile int* can
   B2_CHECK(n > 0, kInternal, "Prefill token ids must be non-empty.");
   B2_CUDA(cudaSetDevice(device));
   const ModelDims& d = model->dims;
+  // Same bound the caller loop enforces before it reaches the executor
+  // (runtime/core/pipeline.cc:249-255), checked before any work is queued.
+  const int would_run = n - 1 + (next_input_token != -1 ? 1 : 0);
+  B2_CHECK(current_step + would_run <= max_num_tokens, kInvalidArgument,
+           "Input token ids are too long. Exceeding the maximum number of tokens allowed: " +
+               std::to_string(current_step + would_run) + " > " + std::to_string(max_num_tokens));
   auto groups = plan_work_groups(d.buckets, d.n_buckets, n);
   last_plan = groups;
   int used = 0;

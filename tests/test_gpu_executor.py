@@ -1,0 +1,168 @@
+"""End-to-end executor parity on a B200 through the C ABI: logits per step (cosine >= 0.999,
+max-abs error <= 2e-2 of the logit range), identical greedy tokens for 16 steps, bit-exact KV
+indexing, and the reference's state-machine behaviour."""
+import numpy as np
+import pytest
+
+from conftest import logits_close, seeded_ids
+
+pytestmark = pytest.mark.gpu
+
+COS_MIN, ERR_MAX = 0.999, 2e-2
+
+
+def run_pair(pkg, orc, models, name, prompt, steps, **kw):
+    cfg, rec, img = models(name)
+    ex = pkg.B200LlmExecutor(img, **kw)
+    ref = orc.OracleExecutor(orc.OracleModel(rec))
+    ex.Prefill(prompt)
+    assert ref.prefill(prompt) == 0
+    out = []
+    for step in range(steps):
+        got = ex.DecodeLogits(None if step == 0 else out[-1][1]).ravel()
+        rc, want = ref.decode_logits(None if step == 0 else out[-1][1])
+        assert rc == 0
+        cos, err = logits_close(got, want)
+        order = np.sort(want)[::-1]
+        out.append((int(np.argmax(got)), int(orc.greedy(want)[0]), cos, err, float(order[0] - order[1])))
+    return ex, ref, out
+
+
+@pytest.mark.parametrize("name,prompt_len,mode,gemm", [
+    ("tiny", 32, 1, 1), ("tiny", 32, 2, 1), ("tiny", 32, 2, 2), ("small", 200, 1, 1), ("small", 200, 2, 2),
+    ("small", 300, 2, 2), ("small-gqa", 150, 2, 2), ("small-gqa", 150, 1, 1),
+])
+def test_logits_and_greedy_tokens_match_oracle(pkg, orc, models, name, prompt_len, mode, gemm):
+    """Teacher-forced on the oracle's token every step, so one flip cannot hide later errors."""
+    cfg, _, _ = models(name)
+    prompt = seeded_ids(0, cfg.vocab, prompt_len)
+    ex, ref, out = run_pair(pkg, orc, models, name, prompt, 16, decode_mode=mode, prefill_gemm=gemm)
+    for step, (tok, want_tok, cos, err, margin) in enumerate(out):
+        assert cos >= COS_MIN and err <= ERR_MAX, (step, cos, err)
+        assert tok == want_tok, (step, tok, want_tok, "oracle top-1/top-2 margin", margin, "err", err)
+    assert ex.GetCurrentStep() == ref.current_step == prompt_len - 1 + 16
+
+
+@pytest.mark.parametrize("name", ["tiny", "small"])
+def test_free_running_greedy_decode(pkg, orc, models, name):
+    """Decode(output_tokens) path: arg-max on the device, token fed back, 16 steps."""
+    cfg, rec, img = models(name)
+    prompt = seeded_ids(1, cfg.vocab, 32)
+    ex = pkg.B200LlmExecutor(img)
+    ref = orc.OracleExecutor(orc.OracleModel(rec))
+    ex.Prefill(prompt)
+    ref.prefill(prompt)
+    got = [ex.Decode() for _ in range(16)]
+    want = [ref.decode_token()[1] for _ in range(16)]
+    assert got == want
+    assert ex.GetCurrentStep() == ref.current_step
+    # the device loop (no host round trip per step) gives the same ids
+    ex2 = pkg.B200LlmExecutor(img)
+    ex2.Prefill(prompt)
+    assert list(ex2.DecodeTokens(16)) == want
+
+
+def test_kv_rows_and_indices(pkg, orc, models):
+    cfg, rec, img = models("small")
+    prompt = seeded_ids(2, cfg.vocab, 300)          # crosses a 256-position page boundary
+    for reversed_pages in (False, True):
+        ex = pkg.B200LlmExecutor(img, reversed_pages=reversed_pages)
+        ref = orc.OracleExecutor(orc.OracleModel(rec))
+        ex.Prefill(prompt)
+        ref.prefill(prompt)
+        ex.Decode(); ref.decode_token()             # one decode-path append at position 299
+        n_pages = (cfg.max_ctx + 255) // 256
+        for pos in (0, 1, 255, 256, 298, 299):
+            for layer in (0, cfg.n_layers - 1):
+                for is_v in (False, True):
+                    row, page, slot = ex.ReadKvRow(layer, is_v, 0, pos)
+                    lp, ls = orc.kv_index(pos)
+                    assert slot == ls and page == (n_pages - 1 - lp if reversed_pages else lp)   # bit-exact
+                    want = ref.read_kv(layer, is_v, 0, pos)
+                    got = row[:cfg.head_dim]
+                    assert np.abs(got - want).max() <= 2e-2 * max(1.0, np.abs(want).max()), (pos, layer, is_v)
+        # rows beyond the written range are untouched
+        row, _, _ = ex.ReadKvRow(0, False, 0, 301)
+        assert np.all(row[:cfg.head_dim] == 0)
+
+
+def test_state_machine_matches_reference_semantics(pkg, orc, models):
+    cfg, rec, img = models("tiny")
+    ex = pkg.B200LlmExecutor(img)
+    ref = orc.OracleExecutor(orc.OracleModel(rec))
+    ids = seeded_ids(3, cfg.vocab, 41)
+    with pytest.raises(pkg.StatusError) as e:
+        ex.DecodeLogits()
+    assert e.value.code == pkg.INVALID_ARGUMENT and "No id available" in e.value.message
+    ex.Prefill(ids); ref.prefill(ids)
+    assert ex.GetLastPrefillPlan() == ref.last_plan() == [(32, 32), (32, 9)]
+    assert ex.GetCurrentStep() == ref.current_step == 41
+    ex.Prefill([7]); ref.prefill([7])               # 1-id prefill replaces the pending id
+    assert ex.GetCurrentStep() == ref.current_step == 41
+    a, b = ex.DecodeLogits().ravel(), ref.decode_logits()[1]
+    cos, err = logits_close(a, b)
+    assert cos >= COS_MIN and err <= ERR_MAX
+    ex.Reset(); ref.reset()
+    assert ex.GetCurrentStep() == 0
+    ex.Prefill(ids[:9]); ref.prefill(ids[:9])       # after Reset old cache rows are unreachable
+    cos, err = logits_close(ex.DecodeLogits().ravel(), ref.decode_logits()[1])
+    assert cos >= COS_MIN and err <= ERR_MAX
+    assert ex.GetVocabSize() == cfg.vocab and ex.GetMaxNumTokens() == cfg.max_ctx
+
+
+def test_capacity_cancel_and_bad_tokens(pkg, models):
+    cfg, _, img = models("tiny")                    # context 64
+    ex = pkg.B200LlmExecutor(img)
+    with pytest.raises(pkg.StatusError) as e:
+        ex.Prefill(np.zeros(70, np.int32))
+    assert e.value.code == pkg.INVALID_ARGUMENT
+    ex.Reset()
+    cancel = np.ones(1, np.int32)
+    with pytest.raises(pkg.StatusError) as e:
+        ex.Prefill(seeded_ids(0, cfg.vocab, 20), cancel=cancel)
+    assert e.value.code == pkg.CANCELLED
+    ex.Reset()
+    with pytest.raises(pkg.StatusError) as e:
+        ex.Prefill(np.array([1, 2, cfg.vocab + 5, 3], np.int32))
+    assert e.value.code == pkg.INVALID_ARGUMENT     # reported through the device error word
+    ex.Reset()
+    ex.Prefill(seeded_ids(0, cfg.vocab, 8))          # the handle stays usable
+    assert 0 <= ex.Decode() < cfg.vocab
+    small = pkg.B200LlmExecutor(img, max_num_tokens=16)
+    assert small.GetMaxNumTokens() == 16
+    small.Prefill(seeded_ids(0, cfg.vocab, 16))
+    small.Decode()
+    with pytest.raises(pkg.StatusError) as e:
+        small.Decode()                               # "Maximum kv-cache size reached."
+    assert e.value.code == pkg.INVALID_ARGUMENT
+
+
+def test_sessions_share_weights_but_not_state(pkg, orc, models):
+    cfg, rec, img = models("small")
+    a = pkg.B200LlmExecutor(img)
+    b = a.CreateShared()
+    pa, pb = seeded_ids(10, cfg.vocab, 40), seeded_ids(11, cfg.vocab, 70)
+    a.Prefill(pa); b.Prefill(pb)
+    ta, tb = [], []
+    for _ in range(8):                              # interleaved decoding
+        ta.append(a.Decode()); tb.append(b.Decode())
+    m = orc.OracleModel(rec)
+    for prompt, got in ((pa, ta), (pb, tb)):
+        ref = orc.OracleExecutor(m)
+        ref.prefill(prompt)
+        assert got == [ref.decode_token()[1] for _ in range(8)]
+
+
+def test_prefill_in_pieces_equals_one_call(pkg, models):
+    cfg, _, img = models("small")
+    ids = seeded_ids(5, cfg.vocab, 330)             # 256-bucket + 74 remainder
+    a, b = pkg.B200LlmExecutor(img), pkg.B200LlmExecutor(img)
+    a.Prefill(ids)
+    b.Prefill(ids[:100]); b.Prefill(ids[100:101]); b.Prefill(ids[101:])
+    # b's 1-id call dropped ids[99] (reference quirk), so compare against the same sequence
+    c = pkg.B200LlmExecutor(img)
+    c.Prefill(np.concatenate([ids[:99], ids[100:]]))
+    lb, lc = b.DecodeLogits().ravel(), c.DecodeLogits().ravel()
+    cos, err = logits_close(lb, lc)
+    assert cos >= 0.9999 and err <= 5e-3
+    assert b.GetCurrentStep() == c.GetCurrentStep() == a.GetCurrentStep() - 1
