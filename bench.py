@@ -185,6 +185,7 @@ def run_reference(args, rank: int) -> None:
 
 
 def main() -> None:
+    global DECODE_STEPS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
@@ -198,7 +199,6 @@ def main() -> None:
     ap.add_argument("--decode-steps", type=int, default=DECODE_STEPS,
                     help="decode steps per bench step (256 is the protocol; fewer only for profiler captures)")
     args = ap.parse_args()
-    global DECODE_STEPS
     DECODE_STEPS = args.decode_steps
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))

@@ -30,7 +30,14 @@ extern "C" {
 
 typedef struct B200LmExecutor B200LmExecutor;
 
-enum { B200LM_DECODE_AUTO = 0, B200LM_DECODE_PHASE_KERNELS = 1, B200LM_DECODE_PERSISTENT = 2 };
+/* decode_mode: AUTO picks the streaming persistent kernel when the model fits its
+ * shared-memory staging, else one kernel per phase replayed from a CUDA graph. */
+enum {
+  B200LM_DECODE_AUTO = 0,
+  B200LM_DECODE_PHASE_KERNELS = 1,     /* one kernel per phase, CUDA graph per step */
+  B200LM_DECODE_PERSISTENT = 2,        /* one cooperative kernel, weights streamed by bulk async copies */
+  B200LM_DECODE_PERSISTENT_BASIC = 3   /* one cooperative kernel, plain loads (comparison) */
+};
 enum { B200LM_GEMM_AUTO = 0, B200LM_GEMM_CHECK = 1, B200LM_GEMM_TCGEN05 = 2 };
 
 typedef struct B200LmConfig {
@@ -114,6 +121,21 @@ int B200Lm_GetLastPrefillPlan(B200LmExecutor* e, int32_t* buckets, int32_t* leng
  * slot the position maps to.  Used by the KV-indexing parity tests. */
 int B200Lm_ReadKvRow(B200LmExecutor* e, int32_t layer, int32_t is_v, int32_t kv_head, int32_t pos,
                      float* out_row, int32_t* out_page, int32_t* out_slot, char** err);
+
+/* Device timeline of ONE greedy decode step run by a persistent decode mode
+ * (equivalent to B200Lm_DecodeToken): for every grid barrier b and CTA c,
+ * stamps[(b * n_cta + c) * 2 + {0,1}] = that SM's cycle counter when the CTA
+ * arrived at / was released from the barrier.  Within one CTA,
+ * arrive[b] - release[b-1] is the time it worked in phase b and
+ * release[b] - arrive[b] the time it waited.  After those n_barriers * n_cta * 2
+ * values come n_barriers * n_cta * 8 stamps taken inside the phase that ends
+ * at barrier b (streaming mode: 0 phase start, 1 staged bytes arrived, 2 next
+ * fill issued, 3 prologue done, 4 MMA done, 5 epilogue done, 6 phase end; 0
+ * where a point was not reached).  The reference has no per-op
+ * profiler hook (only wall-clock BenchmarkInfo marks, runtime/engine/io_types.h:104-163).
+ * capacity is in int64 elements; sm_clock_khz converts cycles to time. */
+int B200Lm_TraceDecodeStep(B200LmExecutor* e, int32_t* out_id, int64_t* stamps, int64_t capacity,
+                           int32_t* n_barriers, int32_t* n_cta, int32_t* sm_clock_khz, char** err);
 
 /* Number of kernels of this library launched on behalf of the handle so far. */
 int B200Lm_GetLaunchCount(B200LmExecutor* e, int64_t* out, char** err);

@@ -30,7 +30,7 @@ FAILED_PRECONDITION, OUT_OF_RANGE, UNIMPLEMENTED, INTERNAL = 9, 11, 12, 13
 _CODE_NAMES = {0: "OK", 1: "CANCELLED", 3: "INVALID_ARGUMENT", 4: "DEADLINE_EXCEEDED", 5: "NOT_FOUND",
                9: "FAILED_PRECONDITION", 11: "OUT_OF_RANGE", 12: "UNIMPLEMENTED", 13: "INTERNAL"}
 
-DECODE_AUTO, DECODE_PHASE_KERNELS, DECODE_PERSISTENT = 0, 1, 2
+DECODE_AUTO, DECODE_PHASE_KERNELS, DECODE_PERSISTENT, DECODE_PERSISTENT_BASIC = 0, 1, 2, 3
 GEMM_AUTO, GEMM_CHECK, GEMM_TCGEN05 = 0, 1, 2
 
 
@@ -54,7 +54,7 @@ _lib: Optional[C.CDLL] = None
 _EXEC_SYMBOLS = ["B200Lm_Create", "B200Lm_CreateShared", "B200Lm_Destroy", "B200Lm_Prefill", "B200Lm_DecodeLogits",
                  "B200Lm_DecodeToken", "B200Lm_DecodeTokens", "B200Lm_Reset", "B200Lm_GetVocabSize",
                  "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_BackendName", "B200Lm_Synchronize",
-                 "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount"]
+                 "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount", "B200Lm_TraceDecodeStep"]
 _OPS_SYMBOLS = ["B200LmOps_RepackW4T", "B200LmOps_RepackW4G", "B200LmOps_UnpackW4", "B200LmOps_GemvW4",
                 "B200LmOps_GemmW4", "B200LmOps_GemmGegluW4", "B200LmOps_Attention"]
 
@@ -85,6 +85,7 @@ def load_library() -> C.CDLL:
         "B200Lm_GetLastPrefillPlan": [vp, vp, vp, i32, vp, errp],
         "B200Lm_ReadKvRow": [vp, i32, i32, i32, i32, vp, vp, vp, errp],
         "B200Lm_GetLaunchCount": [vp, vp, errp],
+        "B200Lm_TraceDecodeStep": [vp, vp, vp, i64, vp, vp, vp, errp],
         "B200LmOps_RepackW4T": [vp, i64, i64, vp, errp],
         "B200LmOps_RepackW4G": [vp, i64, i64, vp, errp],
         "B200LmOps_UnpackW4": [i32, vp, i64, i64, vp, errp],
@@ -222,6 +223,17 @@ class B200LlmExecutor:
         page, slot = C.c_int32(), C.c_int32()
         _call("B200Lm_ReadKvRow", self._h, layer, int(is_v), kv_head, pos, _ptr(row), C.byref(page), C.byref(slot))
         return row, page.value, slot.value
+
+    def TraceDecodeStep(self):
+        """One greedy decode step with the per-barrier device timeline.  Returns (token,
+        stamps[n_barriers, n_cta, 2] in SM cycles, sm_clock_khz)."""
+        cap = 1 << 20
+        buf = np.zeros(cap, dtype=np.int64)
+        tok, nb, nc, khz = C.c_int32(-1), C.c_int32(), C.c_int32(), C.c_int32()
+        _call("B200Lm_TraceDecodeStep", self._h, C.byref(tok), _ptr(buf), cap, C.byref(nb), C.byref(nc), C.byref(khz))
+        n2 = nb.value * nc.value * 2
+        self.last_trace_points = buf[n2:n2 + nb.value * nc.value * 8].reshape(nb.value, nc.value, 8).copy()
+        return tok.value, buf[:n2].reshape(nb.value, nc.value, 2).copy(), khz.value
 
     def GetLaunchCount(self) -> int:
         v = C.c_int64()

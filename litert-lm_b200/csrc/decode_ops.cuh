@@ -11,12 +11,14 @@
 // either as one kernel per phase or inside one persistent cooperative kernel
 // with a grid barrier between phases.
 //
-// int4 GEMV: weights are stored pre-tiled for mma.sync.m16n8k32 (u8 x s8 ->
+// int4 GEMV: weights are stored pre-tiled for mma.sync.m16n8k32 (s8 x s8 ->
 // s32).  Activations are quantised per column to up to three int8 terms
 // (x ~ s*(t0 + t1/128 + t2/16384)), one MMA column per term, so accumulation is
 // exact integer arithmetic (order-independent, hence deterministic) and the
-// result carries ~fp32 accuracy.  Nibbles are stored offset-binary (q + 8); the
-// constant 8*sum(t) is removed in the epilogue.
+// result carries ~fp32 accuracy.  Nibbles are two's complement; masking a
+// nibble into the high half of a byte yields the int8 value 16*q, so the
+// unpack is two logic ops per eight weights and the factor 16 leaves in the
+// epilogue.
 #pragma once
 #include "common.cuh"
 
@@ -35,6 +37,7 @@ struct LayerWeights {
   const float *sqkv, *so, *sgu, *sdown;      // per-output-row scales (sgu in tile order)
   const float *g_pre_attn, *g_post_attn, *g_pre_ffn, *g_post_ffn, *g_q, *g_k;
   int is_global;
+  float gmax_pre_attn, gmax_pre_ffn;   // max |gain| of the two pre-norm gain vectors
   int pad;
 };
 
@@ -67,6 +70,7 @@ struct DecodeArgs {
   const float* embed_scale;           // [vocab]
   const uint4* head_w;                // mma-tiled tied embedding
   const float* g_final;
+  float gmax_final;
   const float *rope_cos[2], *rope_sin[2];   // [max_ctx][hd/2]; 0 local, 1 global
   DecodeState* st;
   // activations (all fp32, device)
@@ -83,15 +87,21 @@ struct DecodeArgs {
   int* step_tokens;     // [capacity][ncols] arg-max of every step since steps_done was reset
   int step_capacity;
   int advance;          // 1: feed arg-max back as next token and bump pos (device loop)
+  long long* trace;     // optional [n_barriers][n_cta][2] SM-clock stamps (arrive, release), or null
+  long long* trace_pts; // optional [n_barriers][n_cta][8] stamps inside the phase that ends at that barrier
 };
+
+// Barrier of the 512 compute threads of a decode CTA (named barrier 1), so a
+// kernel may carry extra warps (a copy producer) that do not take part.
+__device__ __forceinline__ void dec_sync() { asm volatile("bar.sync 1, 512;" ::: "memory"); }
 
 // ----------------------------------------------------------------- reductions
 
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
   v = warp_sum(v);
-  __syncthreads();
+  dec_sync();
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-  __syncthreads();
+  dec_sync();
   float t = 0.f;
 #pragma unroll
   for (int i = 0; i < kDecWarps; ++i) t += scratch[i];
@@ -99,9 +109,9 @@ __device__ __forceinline__ float block_sum(float v, float* scratch) {
 }
 __device__ __forceinline__ float block_max(float v, float* scratch) {
   v = warp_max(v);
-  __syncthreads();
+  dec_sync();
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
-  __syncthreads();
+  dec_sync();
   float t = scratch[0];
 #pragma unroll
   for (int i = 1; i < kDecWarps; ++i) t = fmaxf(t, scratch[i]);
@@ -112,11 +122,11 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
 
 // One 16x64 weight tile is 512 bytes: lane l owns bytes [16l, 16l+16) = words
 // w0..w3.  With g = l/4, t = l%4, word j covers k = 32*(j/2) + 16*(j%2) + 4t + i
-// (i = 0..3): nibble 2i is row g, nibble 2i+1 is row g+8, both stored as q+8.
-__device__ __forceinline__ void mma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+// (i = 0..3): nibble 2i is row g, nibble 2i+1 is row g+8, two's complement.
+__device__ __forceinline__ void mma_s8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                           uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
+      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, "
       "{%0,%1,%2,%3};\n"
       : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -129,7 +139,16 @@ __device__ __forceinline__ int w4t_element(const uint4* tile, int r, int k) {
   int m = k >> 5, half = (k >> 4) & 1, t = (k >> 2) & 3, i = k & 3;
   const uint32_t* words = reinterpret_cast<const uint32_t*>(tile + (g * 4 + t));
   uint32_t w = words[m * 2 + half];
-  return (int)((w >> (8 * i + 4 * hi)) & 0xF) - 8;
+  int v = (int)((w >> (8 * i + 4 * hi)) & 0xF);
+  return v >= 8 ? v - 16 : v;
+}
+
+// Two 16x32 MMAs on one lane's 16 bytes of a tile (words x,y then z,w).
+__device__ __forceinline__ void mma_tile_words(int (&acc)[4], const uint4& w, uint32_t b0, uint32_t b1,
+                                               uint32_t b2, uint32_t b3) {
+  const uint32_t m = 0xF0F0F0F0u;   // high nibble of every byte = 16 * q as int8
+  mma_s8s8(acc, (w.x << 4) & m, w.x & m, (w.y << 4) & m, w.y & m, b0, b1);
+  mma_s8s8(acc, (w.z << 4) & m, w.z & m, (w.w << 4) & m, w.w & m, b2, b3);
 }
 
 struct QuantCols {
@@ -196,9 +215,7 @@ __device__ __forceinline__ void gemv_tiles(const uint4* __restrict__ w, int KT, 
           b2 = *reinterpret_cast<const uint32_t*>(xp + 32);
           b3 = *reinterpret_cast<const uint32_t*>(xp + 48);
         }
-        const uint32_t m = 0x0F0F0F0Fu;
-        mma_u8s8(acc, wv[u].x & m, (wv[u].x >> 4) & m, wv[u].y & m, (wv[u].y >> 4) & m, b0, b1);
-        mma_u8s8(acc, wv[u].z & m, (wv[u].z >> 4) & m, wv[u].w & m, (wv[u].w >> 4) & m, b2, b3);
+        mma_tile_words(acc, wv[u], b0, b1, b2, b3);
       }
     }
   }
@@ -258,6 +275,21 @@ __device__ inline DecodeSmem carve_smem(unsigned char* base, const ModelDims& d,
   return s;
 }
 
+// Quantises one value with scale inv into up to three int8 terms.
+__device__ __forceinline__ void quantize_value(float r, int nterms, int8_t* q0, int stride) {
+  float t0 = fminf(fmaxf(rintf(r), -127.f), 127.f);
+  q0[0] = (int8_t)(int)t0;
+  if (nterms > 1) {
+    float r1 = (r - t0) * 128.0f;
+    float t1 = fminf(fmaxf(rintf(r1), -127.f), 127.f);
+    q0[stride] = (int8_t)(int)t1;
+    if (nterms > 2) {
+      float r2 = (r1 - t1) * 128.0f;
+      q0[2 * stride] = (int8_t)(int)fminf(fmaxf(rintf(r2), -127.f), 127.f);
+    }
+  }
+}
+
 // Quantises xf[ncols][K] (shared) into xq with nterms int8 terms per column.
 __device__ inline void quantize_cols(const DecodeSmem& s, int K, int ncols, int nterms) {
   for (int col = 0; col < ncols; ++col) {
@@ -266,49 +298,21 @@ __device__ inline void quantize_cols(const DecodeSmem& s, int K, int ncols, int 
     for (int i = threadIdx.x; i < K; i += kDecThreads) m = fmaxf(m, fabsf(x[i]));
     m = block_max(m, s.scratch);
     float inv = m > 0.f ? 127.0f / m : 0.f;
-    int s0 = 0, s1 = 0, s2 = 0;
     int8_t* q0 = s.xq + (size_t)(col * nterms) * s.xstride;
-    for (int i = threadIdx.x; i < K; i += kDecThreads) {
-      float r = x[i] * inv;
-      float t0 = fminf(fmaxf(rintf(r), -127.f), 127.f);
-      q0[i] = (int8_t)(int)t0;
-      s0 += (int)t0;
-      if (nterms > 1) {
-        float r1 = (r - t0) * 128.0f;
-        float t1 = fminf(fmaxf(rintf(r1), -127.f), 127.f);
-        q0[s.xstride + i] = (int8_t)(int)t1;
-        s1 += (int)t1;
-        if (nterms > 2) {
-          float r2 = (r1 - t1) * 128.0f;
-          float t2 = fminf(fmaxf(rintf(r2), -127.f), 127.f);
-          q0[2 * s.xstride + i] = (int8_t)(int)t2;
-          s2 += (int)t2;
-        }
-      }
-    }
-    // Exact integer column sums (fp32 holds them exactly: |sum| < 2^24).
-    float f0 = block_sum((float)s0, s.scratch);
-    float f1 = block_sum((float)s1, s.scratch);
-    float f2 = block_sum((float)s2, s.scratch);
-    if (threadIdx.x == 0) {
-      s.colscale[col] = m > 0.f ? m / 127.0f : 0.f;
-      s.colsum[col * nterms] = (int)f0;
-      if (nterms > 1) s.colsum[col * nterms + 1] = (int)f1;
-      if (nterms > 2) s.colsum[col * nterms + 2] = (int)f2;
-    }
+    for (int i = threadIdx.x; i < K; i += kDecThreads) quantize_value(x[i] * inv, nterms, q0 + i, s.xstride);
+    if (threadIdx.x == 0) s.colscale[col] = m > 0.f ? m / 127.0f : 0.f;
   }
-  __syncthreads();
+  dec_sync();
 }
 
 // Value of output (unit, row, col) after a round: sum over terms, bias removed.
 __device__ __forceinline__ float finalize_value(const DecodeSmem& s, int unit, int row, int col,
                                                 int nterms) {
   const int* r = s.red + (unit * 16 + row) * kQCols + col * nterms;
-  const int* cs = s.colsum + col * nterms;
-  float v = (float)(r[0] - 8 * cs[0]);
-  if (nterms > 1) v += (float)(r[1] - 8 * cs[1]) * (1.0f / 128.0f);
-  if (nterms > 2) v += (float)(r[2] - 8 * cs[2]) * (1.0f / 16384.0f);
-  return v * s.colscale[col];
+  float v = (float)r[0];
+  if (nterms > 1) v += (float)r[1] * (1.0f / 128.0f);
+  if (nterms > 2) v += (float)r[2] * (1.0f / 16384.0f);
+  return v * (s.colscale[col] * (1.0f / 16.0f));      // weights entered the MMA as 16 * q
 }
 
 enum GemvEpilogue { kEpiPlain = 0, kEpiGeglu = 1, kEpiHead = 2 };
@@ -352,9 +356,9 @@ __device__ inline void gemv_run(const GemvJob& j, const DecodeSmem& s, int ncols
   for (int r0 = t0; r0 < t1; r0 += kMaxRoundUnits) {
     int nu = min(kMaxRoundUnits, t1 - r0);
     for (int i = threadIdx.x; i < nu * 16 * kQCols; i += kDecThreads) s.red[i] = 0;
-    __syncthreads();
+    dec_sync();
     gemv_tiles(j.w, KT, kt0, ktn, r0, nu, xc, s.red);
-    __syncthreads();
+    dec_sync();
     if (j.epilogue == kEpiGeglu) {
       int npair = nu / 2;
       for (int i = threadIdx.x; i < npair * 16 * ncols; i += kDecThreads) {
@@ -380,7 +384,7 @@ __device__ inline void gemv_run(const GemvJob& j, const DecodeSmem& s, int ncols
         }
       }
     }
-    __syncthreads();
+    dec_sync();
   }
 }
 
@@ -413,7 +417,7 @@ __device__ inline void prologue_resid_norm(const DecodeArgs& a, const DecodeSmem
     float r2 = rsqrtf(ss2 / (float)d + a.dims.eps);
     for (int i = threadIdx.x; i < d; i += kDecThreads) x[i] = x[i] * r2 * g_pre[i];
   }
-  __syncthreads();
+  dec_sync();
 }
 
 // x = dequant(E[token]) * sqrt(d) ; xout <- x (cta 0) ; xf <- rmsnorm(x) * g_pre
@@ -444,7 +448,7 @@ __device__ inline void prologue_embed_norm(const DecodeArgs& a, const DecodeSmem
     float r = rsqrtf(ss / (float)d + a.dims.eps);
     for (int i = threadIdx.x; i < d; i += kDecThreads) x[i] = x[i] * r * g_pre[i];
   }
-  __syncthreads();
+  dec_sync();
 }
 
 // ------------------------------------------------------------------ attention
@@ -487,6 +491,29 @@ __device__ __forceinline__ void load_head_row(const T* __restrict__ p, int lane,
     }
   }
 }
+// Same element mapping, source in shared memory (rows staged there by bulk copies).
+template <typename T, int HD>
+__device__ __forceinline__ void load_head_row_smem(const T* p, int lane, float (&out)[HD / 32]) {
+  constexpr int VEC = HD / 32;
+  if constexpr (HD >= 128) {
+#pragma unroll
+    for (int i = 0; i < HD / 128; ++i) {
+      if constexpr (sizeof(T) == 4) {
+        float4 v = *reinterpret_cast<const float4*>(p + i * 128 + lane * 4);
+        out[i * 4 + 0] = v.x; out[i * 4 + 1] = v.y; out[i * 4 + 2] = v.z; out[i * 4 + 3] = v.w;
+      } else {
+        uint2 v = *reinterpret_cast<const uint2*>(p + i * 128 + lane * 4);
+        __nv_bfloat162 a = *reinterpret_cast<__nv_bfloat162*>(&v.x);
+        __nv_bfloat162 b = *reinterpret_cast<__nv_bfloat162*>(&v.y);
+        out[i * 4 + 0] = __low2float(a); out[i * 4 + 1] = __high2float(a);
+        out[i * 4 + 2] = __low2float(b); out[i * 4 + 3] = __high2float(b);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) out[c] = kv_to_float<T>(p[lane * VEC + c]);
+  }
+}
 template <int HD>
 __device__ __forceinline__ int head_elem(int lane, int c) {
   if constexpr (HD >= 128) return (c >> 2) * 128 + lane * 4 + (c & 3);
@@ -510,7 +537,24 @@ struct AttnJob {
   float* out_f32;            // [nq_tokens][hq][hd] normalised output (needs nsplit == 1), optional
   __nv_bfloat16* out_bf16;   // same in bf16, optional
   int* err;
+  // optional staging (streaming decode kernel): rows of keys k0 .. k0+npre-1 of this
+  // split already sit in shared memory, as does the RoPE row of the query position
+  const void* k_pre;
+  const void* v_pre;
+  int npre;
+  int rope_is_row;           // cosT / sinT point at the row of `pos`, not at the table
+  int max_warps;             // > 0: only this many warps walk keys (smaller merge area)
 };
+
+// Key range [k0, k1) of one split.
+__device__ __forceinline__ void attn_split_range(const ModelDims& dm, int pos, int is_global, int nsplit,
+                                                 int split, int* k0, int* k1) {
+  int nkeys = is_global ? pos + 1 : min(pos + 1, dm.window);
+  int lo = pos + 1 - nkeys;
+  int chunk = (nkeys + nsplit - 1) / nsplit;
+  *k0 = lo + split * chunk;
+  *k1 = min(*k0 + chunk, pos + 1);
+}
 
 // One (query, kv head, split) work item: all G query heads of the group share
 // every K/V row that is loaded.
@@ -519,7 +563,8 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
                                  int split) {
   constexpr int VEC = HD / 32;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nwarps = blockDim.x >> 5;
+  const int nwarps_all = blockDim.x >> 5;
+  const int nwarps = (j.max_warps > 0 && j.max_warps < nwarps_all) ? j.max_warps : nwarps_all;
   const int half = HD / 2;
   int pos = j.pos ? __ldcg(j.pos + qi) : j.pos0 + qi;
   if (pos < 0 || pos >= dm.max_ctx) {
@@ -536,7 +581,7 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
   const float* row = j.qkv + (size_t)qi * dm.nqkv();
   const float att_scale = rsqrtf((float)HD);
   const int nheads_stage = j.appended ? G : G + 2;
-  for (int h = warp; h < nheads_stage; h += nwarps) {
+  for (int h = warp; h < nheads_stage; h += nwarps_all) {
     if (h <= G) {   // q heads 0..G-1, k head at G
       const float* src = h < G ? row + (size_t)(kvh * G + h) * HD : row + dm.nq() + (size_t)kvh * HD;
       const float* gain = h < G ? j.g_q : j.g_k;
@@ -553,7 +598,11 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
         float a0 = __ldcg(src + e) * r * (gain ? gain[e] : 1.0f);
         float b0 = __ldcg(src + e + half) * r * (gain ? gain[e + half] : 1.0f);
         float cs = 1.0f, sn = 0.0f;
-        if (j.cosT) { cs = j.cosT[(size_t)pos * half + e]; sn = j.sinT[(size_t)pos * half + e]; }
+        if (j.cosT) {
+          size_t ri = j.rope_is_row ? (size_t)e : (size_t)pos * half + e;
+          cs = j.cosT[ri];
+          sn = j.sinT[ri];
+        }
         dst[e] = (a0 * cs - b0 * sn) * post;
         dst[e + half] = (b0 * cs + a0 * sn) * post;
       }
@@ -581,13 +630,15 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
         vbase[off + e] = __float2bfloat16(v_s[e]);
       }
     }
+    // later steps fetch these rows with bulk async copies
+    asm volatile("fence.proxy.async.global;" ::: "memory");
   }
   // key range of this split
-  int nkeys = j.is_global ? pos + 1 : min(pos + 1, dm.window);
-  int lo = pos + 1 - nkeys;
-  int chunk = (nkeys + j.nsplit - 1) / j.nsplit;
-  int k0 = lo + split * chunk;
-  int k1 = min(k0 + chunk, pos + 1);
+  int k0, k1;
+  attn_split_range(dm, pos, j.is_global, j.nsplit, split, &k0, &k1);
+  const T* kpre = reinterpret_cast<const T*>(j.k_pre);
+  const T* vpre = reinterpret_cast<const T*>(j.v_pre);
+  const int kend = warp < nwarps ? k1 : k0;     // idle warps walk no keys
   float q[G][VEC], o[G][VEC], m[G], l[G];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -599,9 +650,9 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
       o[g][c] = 0.f;
     }
   }
-  for (int ka = k0 + warp; ka < k1; ka += 2 * nwarps) {
+  for (int ka = k0 + warp; ka < kend; ka += 2 * nwarps) {
     int kb = ka + nwarps;
-    bool hasb = kb < k1;
+    bool hasb = kb < kend;
     float kA[VEC], kB[VEC], vA[VEC], vB[VEC];
     {
       size_t offa = (((size_t)ptab[ka / kPage] * dm.hkv + kvh) * kPage + (ka % kPage)) * HD;
@@ -615,6 +666,9 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
             vA[c] = __bfloat162float(__float2bfloat16(vA[c]));
           }
         }
+      } else if (ka - k0 < j.npre) {
+        load_head_row_smem<T, HD>(kpre + (size_t)(ka - k0) * HD, lane, kA);
+        load_head_row_smem<T, HD>(vpre + (size_t)(ka - k0) * HD, lane, vA);
       } else {
         load_head_row<T, HD>(kbase + offa, lane, kA);
         load_head_row<T, HD>(vbase + offa, lane, vA);
@@ -631,6 +685,9 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
               vB[c] = __bfloat162float(__float2bfloat16(vB[c]));
             }
           }
+        } else if (kb - k0 < j.npre) {
+          load_head_row_smem<T, HD>(kpre + (size_t)(kb - k0) * HD, lane, kB);
+          load_head_row_smem<T, HD>(vpre + (size_t)(kb - k0) * HD, lane, vB);
         } else {
           load_head_row<T, HD>(kbase + offb, lane, kB);
           load_head_row<T, HD>(vbase + offb, lane, vB);
@@ -659,11 +716,13 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
     }
   }
   // merge the warps of this CTA
+  if (warp < nwarps) {
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) { wm[warp * G + g] = m[g]; wl[warp * G + g] = l[g]; }
+    for (int g = 0; g < G; ++g) {
+      if (lane == 0) { wm[warp * G + g] = m[g]; wl[warp * G + g] = l[g]; }
 #pragma unroll
-    for (int c = 0; c < VEC; ++c) wo[((size_t)warp * G + g) * HD + head_elem<HD>(lane, c)] = o[g][c];
+      for (int c = 0; c < VEC; ++c) wo[((size_t)warp * G + g) * HD + head_elem<HD>(lane, c)] = o[g][c];
+    }
   }
   __syncthreads();
   for (int i = threadIdx.x; i < G * HD; i += blockDim.x) {
@@ -745,6 +804,11 @@ __device__ inline AttnJob make_decode_attn_job(const DecodeArgs& a, int layer) {
   j.out_f32 = nullptr;
   j.out_bf16 = nullptr;
   j.err = &a.st->err;
+  j.k_pre = nullptr;
+  j.v_pre = nullptr;
+  j.npre = 0;
+  j.rope_is_row = 0;
+  j.max_warps = 0;
   return j;
 }
 
@@ -803,7 +867,7 @@ __device__ inline void phase_oproj(const DecodeArgs& a, const DecodeSmem& s, int
       s.xf[(size_t)col * Ks + i] = Ls > 0.f ? O / Ls : 0.f;
     }
   }
-  __syncthreads();
+  dec_sync();
   quantize_cols(s, Ks, a.ncols, a.nterms);
   gemv_run(j, s, a.ncols, a.nterms, slice, t0, t1, nullptr, nullptr);
 }
@@ -829,7 +893,7 @@ __device__ inline void phase_down(const DecodeArgs& a, const DecodeSmem& s, int 
   for (int col = 0; col < a.ncols; ++col)
     for (int i = threadIdx.x; i < Ks; i += kDecThreads)
       s.xf[(size_t)col * Ks + i] = __ldcg(a.act + (size_t)col * a.dims.ffn + (size_t)slice * Ks + i);
-  __syncthreads();
+  dec_sync();
   quantize_cols(s, Ks, a.ncols, a.nterms);
   gemv_run(j, s, a.ncols, a.nterms, slice, t0, t1, nullptr, nullptr);
 }
@@ -853,10 +917,10 @@ __device__ inline void phase_head(const DecodeArgs& a, const DecodeSmem& s, int 
   float* sv = s.argbuf;
   int* si = reinterpret_cast<int*>(s.argbuf + kDecThreads);
   for (int col = 0; col < a.ncols; ++col) {
-    __syncthreads();
+    dec_sync();
     sv[threadIdx.x] = bv[col];
     si[threadIdx.x] = bi[col];
-    __syncthreads();
+    dec_sync();
     for (int st = kDecThreads / 2; st > 0; st >>= 1) {
       if (threadIdx.x < st) {
         float ov = sv[threadIdx.x + st];
@@ -866,7 +930,7 @@ __device__ inline void phase_head(const DecodeArgs& a, const DecodeSmem& s, int 
           si[threadIdx.x] = oi;
         }
       }
-      __syncthreads();
+      dec_sync();
     }
     if (threadIdx.x == 0) {
       a.amax_val[(size_t)cta * a.ncols + col] = sv[0];
@@ -911,7 +975,7 @@ __device__ inline void phase_argmax(const DecodeArgs& a, int ncta_head) {
 enum DecodePhase { kPhQkv = 0, kPhAttn, kPhOproj, kPhGateUp, kPhDown, kPhHead, kPhArgmax };
 
 __global__ void __launch_bounds__(kDecThreads, 1)
-decode_phase_kernel(DecodeArgs a, int phase, int layer) {
+decode_phase_kernel(const __grid_constant__ DecodeArgs a, int phase, int layer) {
   extern __shared__ __align__(16) unsigned char dsm[];
   DecodeSmem s = carve_smem(dsm, a.dims, a.ncols);
   const int cta = blockIdx.x, ncta = gridDim.x;
@@ -931,10 +995,12 @@ decode_phase_kernel(DecodeArgs a, int phase, int layer) {
 // Sense-free counting barrier: every CTA adds one and waits for the count to
 // reach the next multiple of the grid size.  The wait is bounded; on give-up
 // the error word is set and the kernel runs to completion without waiting again.
-__device__ __forceinline__ void grid_barrier(DecodeState* st, unsigned int* epoch, int ncta) {
-  __syncthreads();
+__device__ __forceinline__ void grid_barrier(DecodeState* st, unsigned int* epoch, int ncta,
+                                             long long* trace = nullptr, int bar_idx = 0) {
+  dec_sync();
   if (threadIdx.x == 0) {
     *epoch += (unsigned)ncta;
+    if (trace) trace[((size_t)bar_idx * ncta + blockIdx.x) * 2] = clock64();
     __threadfence();
     atomicAdd(&st->barrier, 1u);
     unsigned int target = *epoch;
@@ -943,41 +1009,44 @@ __device__ __forceinline__ void grid_barrier(DecodeState* st, unsigned int* epoc
       unsigned int v;
       asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(&st->barrier));
       if ((int)(v - target) >= 0) break;
-      if (*reinterpret_cast<volatile int*>(&st->err) == (int)kDevBarrierTimeout) break;
-      if (++spins > 4000000L) {   // ~ a second; never reached in a healthy run
+      ++spins;
+      if ((spins & 255) == 0 && *reinterpret_cast<volatile int*>(&st->err) == (int)kDevBarrierTimeout) break;
+      if (spins > 4000000L) {   // ~ a second; never reached in a healthy run
         atomicExch(&st->err, (int)kDevBarrierTimeout);
         break;
       }
     }
+    if (trace) trace[((size_t)bar_idx * ncta + blockIdx.x) * 2 + 1] = clock64();
   }
-  __syncthreads();
+  dec_sync();
 }
 
 __global__ void __launch_bounds__(kDecThreads, 1)
-decode_persistent_kernel(DecodeArgs a, int nsteps, unsigned int epoch0) {
+decode_persistent_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned int epoch0) {
   extern __shared__ __align__(16) unsigned char dsm[];
   DecodeSmem s = carve_smem(dsm, a.dims, a.ncols);
   __shared__ unsigned int epoch;
   if (threadIdx.x == 0) epoch = epoch0;
-  __syncthreads();
+  dec_sync();
   const int cta = blockIdx.x, ncta = gridDim.x;
+  int bar = 0;
   for (int step = 0; step < nsteps; ++step) {
     for (int layer = 0; layer < a.dims.n_layers; ++layer) {
       phase_qkv(a, s, layer, cta, ncta);
-      grid_barrier(a.st, &epoch, ncta);
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
       phase_attn(a, s, layer, cta, ncta);
-      grid_barrier(a.st, &epoch, ncta);
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
       phase_oproj(a, s, layer, cta, ncta);
-      grid_barrier(a.st, &epoch, ncta);
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
       phase_gateup(a, s, layer, cta, ncta);
-      grid_barrier(a.st, &epoch, ncta);
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
       phase_down(a, s, layer, cta, ncta);
-      grid_barrier(a.st, &epoch, ncta);
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
     }
     phase_head(a, s, cta, ncta);
-    grid_barrier(a.st, &epoch, ncta);
+    grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
     if (cta == 0) phase_argmax(a, ncta);
-    grid_barrier(a.st, &epoch, ncta);
+    grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
   }
 }
 

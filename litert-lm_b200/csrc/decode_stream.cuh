@@ -1,0 +1,1013 @@
+// Streaming persistent decode kernel.
+//
+// Same phases as decode_ops.cuh (A qkv, B attention, C o-proj, D gate/up, E down,
+// H head), one cooperative launch for one or more steps, a grid barrier between
+// phases.  What differs is where the bytes come from and who fetches them:
+//
+//  * every read of HBM-resident data -- int4 weight tiles, their scales, norm
+//    gains, cached K/V rows, the RoPE row -- arrives as 1-D bulk async copies
+//    (cp.async.bulk, completion on an mbarrier) in a two-halves staging area in
+//    shared memory, one or two "fills" ahead of its use;
+//  * a dedicated PRODUCER WARP walks the static fill sequence on its own
+//    (full / empty mbarriers per half, a small descriptor per fill published in
+//    shared memory), so the 16 compute warps never compute addresses or issue
+//    copies: after a grid barrier they touch L2-resident activations and shared
+//    memory only;
+//  * the norm prologues need ONE block reduction: with f the incoming branch
+//    output and x = xin + rmsnorm(f) g_post, the sums of f^2, xin^2, xin f g_post
+//    and (f g_post)^2 give both RMS factors; activations are quantised against
+//    the static bound |rmsnorm(x)_i g_i| <= sqrt(d) max|g|, so no max-reduction.
+//
+// Fills form one static sequence per CTA: for every phase max(1, rounds) fills,
+// fill n lands in half n & 1 and completes full[n & 1] exactly once (empty fills
+// just arrive), consumers release the half through empty[n & 1].
+#pragma once
+#include "common.cuh"
+#include "decode_ops.cuh"
+#include "prefill_ops.cuh"
+
+namespace b200lm {
+
+#define B2_TP(k)                                                                          \
+  do {                                                                                    \
+    if (a.trace_pts && threadIdx.x == 0)                                                  \
+      a.trace_pts[((size_t)bar * gridDim.x + blockIdx.x) * 8 + (k)] = clock64();          \
+  } while (0)
+
+enum StreamPhase { kSA = 0, kSB = 1, kSC = 2, kSD = 3, kSE = 4, kSH = 5 };
+constexpr int kStreamThreads = kDecThreads + 32;   // 16 compute warps + 1 producer warp
+constexpr int kStreamMaxStagedRows = 1024;         // cap on K/V rows staged per chunk
+constexpr int kMaxV4 = 3;                          // float4 per thread held in registers by the norm prologue
+
+struct PhasePlan {     // this CTA's share of one GEMV phase
+  int N, K, slices, epilogue, has_gains;
+  int work, slice, t0, t1, ktn, tpr, rounds;
+};
+
+struct StreamCursor {
+  int step, layer, ph, round;
+};
+
+struct FillDesc {      // published by the producer for the consumers of one fill
+  int ph, layer, round, valid;
+  int ta, ntile, ktn, has_gains;          // GEMV fills
+  int col, kvh, split, nsplit, k0, npre, is_global, pad;   // attention fills
+};
+
+struct StreamCtx {
+  DecodeSmem s;                 // activation staging shared with the per-phase kernels
+  unsigned char* half[2];
+  int half_bytes;
+  uint64_t* full;               // [2] bytes of a fill have landed
+  uint64_t* empty;              // [2] consumers are done with the half
+  uint64_t* aux;                // synchronous fetches inside the attention phase
+  FillDesc* slot;               // [2]
+  volatile int* step_ready;     // steps whose token / position are final
+  LayerWeights* lw;             // [n_layers] copy in shared memory
+  LayerKv* lkv;                 // [n_layers]
+  PhasePlan* plan;              // [6] indexed by StreamPhase (kSB unused)
+  int npre_max;                 // K/V rows a half can hold
+  unsigned wait_no;             // fills consumed
+  unsigned aux_cnt;
+};
+
+__host__ __device__ inline int stream_kmax(const ModelDims& d) {
+  int kmax = d.ffn > d.d ? d.ffn : d.d;
+  if (d.hq * d.hd > kmax) kmax = d.hq * d.hd;
+  return kmax;
+}
+
+__host__ __device__ inline size_t stream_attn_bytes(const ModelDims& d) {
+  int G = d.hq / d.hkv;
+  return ((size_t)(G + 2) * d.hd + (size_t)G * (kStreamMaxStagedRows + 1) + 4 * G) * 4;
+}
+
+__host__ __device__ inline size_t stream_fixed_bytes(const ModelDims& d, int ncols) {
+  int kmax = stream_kmax(d);
+  size_t act = (size_t)ncols * kmax * 4;                          // xf
+  act += (size_t)ncols * 3 * dec_xstride(kmax);                   // xq (three terms)
+  act += (size_t)kMaxRoundUnits * 16 * kQCols * 4;                // red
+  size_t attn = stream_attn_bytes(d);
+  if (attn > act) act = attn;                                     // attention aliases the GEMV staging
+  size_t b = act + 64 * 4 + kMaxCols * 4 + 2 * kDecThreads * 4;   // scratch, colscale, argbuf
+  b += (size_t)d.n_layers * (sizeof(LayerWeights) + sizeof(LayerKv)) + 6 * sizeof(PhasePlan);
+  b += 128 + 2 * sizeof(FillDesc) + 64;                           // mbarriers, descriptors, flags
+  return b + 1024;
+}
+
+__device__ __forceinline__ void stream_carve(unsigned char* base, const ModelDims& d, int ncols, int half_bytes,
+                                             StreamCtx& c) {
+  unsigned char* p = reinterpret_cast<unsigned char*>(((uintptr_t)base + 127) & ~(uintptr_t)127);
+  c.half[0] = p; p += half_bytes;
+  c.half[1] = p; p += half_bytes;
+  c.half_bytes = half_bytes;
+  c.full = reinterpret_cast<uint64_t*>(p);
+  c.empty = c.full + 2;
+  c.aux = c.full + 4;
+  p += 128;
+  c.slot = reinterpret_cast<FillDesc*>(p); p += 2 * sizeof(FillDesc);
+  c.step_ready = reinterpret_cast<volatile int*>(p); p += 64;
+  int kmax = stream_kmax(d);
+  unsigned char* act0 = p;
+  c.s.xf = reinterpret_cast<float*>(p); p += (size_t)ncols * kmax * 4;
+  c.s.xstride = dec_xstride(kmax);
+  c.s.xq = reinterpret_cast<int8_t*>(p); p += (size_t)ncols * 3 * c.s.xstride;
+  c.s.red = reinterpret_cast<int*>(p); p += (size_t)kMaxRoundUnits * 16 * kQCols * 4;
+  size_t attn = stream_attn_bytes(d);
+  if ((size_t)(p - act0) < attn) p = act0 + attn;
+  p = reinterpret_cast<unsigned char*>(((uintptr_t)p + 15) & ~(uintptr_t)15);
+  c.s.attn = reinterpret_cast<float*>(act0);
+  c.s.scratch = reinterpret_cast<float*>(p); p += 64 * 4;
+  c.s.colscale = reinterpret_cast<float*>(p); p += kMaxCols * 4;
+  c.s.colsum = nullptr;
+  c.s.argbuf = reinterpret_cast<float*>(p); p += 2 * kDecThreads * 4;
+  c.lw = reinterpret_cast<LayerWeights*>(p); p += (size_t)d.n_layers * sizeof(LayerWeights);
+  c.lkv = reinterpret_cast<LayerKv*>(p); p += (size_t)d.n_layers * sizeof(LayerKv);
+  c.plan = reinterpret_cast<PhasePlan*>(p);
+}
+
+__host__ __device__ inline void stream_phase_shape(const ModelDims& d, int o_slices, int down_slices, int ph, int* N,
+                                                   int* K, int* slices, int* epi, int* gains) {
+  switch (ph) {
+    case kSA: *N = d.nqkv(); *K = d.d; *slices = 1; *epi = kEpiPlain; *gains = 1; break;
+    case kSC: *N = d.d; *K = d.nq(); *slices = o_slices; *epi = kEpiPlain; *gains = 0; break;
+    case kSD: *N = 2 * d.ffn; *K = d.d; *slices = 1; *epi = kEpiGeglu; *gains = 1; break;
+    case kSE: *N = d.d; *K = d.ffn; *slices = down_slices; *epi = kEpiPlain; *gains = 0; break;
+    default: *N = d.vocab; *K = d.d; *slices = 1; *epi = kEpiHead; *gains = 1; break;
+  }
+}
+
+// Tiles of one phase that fit one staging half (0: the model does not fit this kernel).
+__host__ __device__ inline int stream_tiles_per_round(const ModelDims& d, int half_bytes, int K, int slices, int epi,
+                                                      int gains) {
+  int ktn = K / 64 / slices;
+  int cap = half_bytes - (gains ? 2 * d.d * 4 : 0);
+  int per_tile = ktn * 512 + 64;
+  int tpr = cap / per_tile;
+  if (tpr > kMaxRoundUnits) tpr = kMaxRoundUnits;
+  if (epi == kEpiGeglu) tpr &= ~1;
+  return tpr;
+}
+
+__host__ inline bool stream_model_fits(const ModelDims& d, int o_slices, int down_slices, int half_bytes) {
+  const int phases[5] = {kSA, kSC, kSD, kSE, kSH};
+  for (int ph : phases) {
+    int N, K, sl, epi, gains;
+    stream_phase_shape(d, o_slices, down_slices, ph, &N, &K, &sl, &epi, &gains);
+    if (stream_tiles_per_round(d, half_bytes, K, sl, epi, gains) < (epi == kEpiGeglu ? 2 : 1)) return false;
+  }
+  if (d.d / 4 > kMaxV4 * kDecThreads) return false;
+  if (d.hq / d.hkv * d.hd > 2 * kDecThreads) return false;
+  int esz = d.kv_dtype == 0 ? 4 : 2;
+  return half_bytes >= 2 * d.hd * esz + d.hd * 4 + 64;   // at least one staged K/V row pair + RoPE row
+}
+
+__device__ __forceinline__ void stream_make_plans(const DecodeArgs& a, StreamCtx& c, int cta, int ncta) {
+  const int phases[5] = {kSA, kSC, kSD, kSE, kSH};
+  for (int i = 0; i < 5; ++i) {
+    PhasePlan& p = c.plan[phases[i]];
+    stream_phase_shape(a.dims, a.o_slices, a.down_slices, phases[i], &p.N, &p.K, &p.slices, &p.epilogue, &p.has_gains);
+    GemvJob j{nullptr, nullptr, p.N, p.K, p.slices, nullptr, p.epilogue};
+    p.work = gemv_assignment(j, cta, ncta, &p.slice, &p.t0, &p.t1) ? 1 : 0;
+    p.ktn = p.K / 64 / p.slices;
+    p.tpr = stream_tiles_per_round(a.dims, c.half_bytes, p.K, p.slices, p.epilogue, p.has_gains);
+    p.rounds = p.work ? (p.t1 - p.t0 + p.tpr - 1) / p.tpr : 0;
+  }
+}
+
+__device__ __forceinline__ void stream_advance(StreamCursor& cur, const StreamCtx& c, int n_layers) {
+  int fills = cur.ph == kSB ? 1 : (c.plan[cur.ph].rounds > 1 ? c.plan[cur.ph].rounds : 1);
+  if (++cur.round < fills) return;
+  cur.round = 0;
+  if (cur.ph == kSH) { cur.ph = kSA; cur.layer = 0; ++cur.step; return; }
+  if (cur.ph == kSE) {
+    if (cur.layer + 1 < n_layers) { ++cur.layer; cur.ph = kSA; } else { cur.ph = kSH; }
+    return;
+  }
+  ++cur.ph;
+}
+
+// ------------------------------------------------------------ producer warp
+
+__device__ __forceinline__ void stream_producer(const DecodeArgs& a, StreamCtx& c, int cta, int nsteps) {
+  const int lane = threadIdx.x & 31;
+  const ModelDims& dm = a.dims;
+  const int last = dm.n_layers - 1;
+  StreamCursor cur{0, 0, kSA, 0};
+  for (unsigned n = 0; cur.step < nsteps; ++n) {
+    const unsigned h = n & 1u;
+    if (n >= 2 && !mbar_wait(&c.empty[h], ((n >> 1) - 1u) & 1u, &a.st->err)) return;
+    unsigned char* dst = c.half[h];
+    uint64_t* bar = &c.full[h];
+    FillDesc d;
+    d.ph = cur.ph; d.layer = cur.layer; d.round = cur.round; d.valid = 0;
+    d.ta = d.ntile = d.ktn = d.has_gains = 0;
+    d.col = d.kvh = d.split = d.nsplit = d.k0 = d.npre = d.is_global = d.pad = 0;
+    if (cur.ph == kSB) {
+      // token / position of this step must be final before its rows are chosen
+      for (long spins = 0; *c.step_ready <= cur.step; ++spins) {
+        __nanosleep(40);
+        if (spins > 20000000L) { atomicExch(&a.st->err, (int)kDevBarrierTimeout); return; }
+      }
+      d.is_global = c.lw[cur.layer].is_global;
+      d.nsplit = d.is_global ? a.n_attn_splits_global : a.n_attn_splits_local;
+      const int items = a.ncols * dm.hkv * d.nsplit;
+      if (cta < items) {
+        d.valid = 1;
+        d.split = cta % d.nsplit;
+        int rest = cta / d.nsplit;
+        d.kvh = rest % dm.hkv;
+        d.col = rest / dm.hkv;
+        int pos = __ldcg(&a.st->pos[d.col]);
+        if (pos < 0 || pos >= dm.max_ctx) pos = 0;
+        int k0, k1;
+        attn_split_range(dm, pos, d.is_global, d.nsplit, d.split, &k0, &k1);
+        d.k0 = k0;
+        int nold = min(k1, pos) - k0;        // the row of `pos` itself is not in the cache yet
+        d.npre = nold < 0 ? 0 : min(nold, c.npre_max);
+        if (lane == 0) c.slot[h] = d;
+        __syncwarp();
+        const int esz = dm.kv_dtype == 0 ? 4 : 2;
+        const uint32_t row = (uint32_t)dm.hd * esz;
+        const uint32_t rope_row = (uint32_t)(dm.hd / 2) * 4;
+        if (lane == 0) mbar_arrive_expect_tx(bar, 2u * d.npre * row + 2u * rope_row);
+        __syncwarp();
+        const int* ptab = a.page_table + (size_t)d.col * a.pages_per_seq;
+        const unsigned char* kb = reinterpret_cast<const unsigned char*>(c.lkv[cur.layer].k);
+        const unsigned char* vb = reinterpret_cast<const unsigned char*>(c.lkv[cur.layer].v);
+        for (int i = lane; i < 2 * d.npre; i += 32) {
+          int r = i >> 1, isv = i & 1, key = d.k0 + r;
+          size_t off = ((((size_t)ptab[key / kPage] * dm.hkv + d.kvh) * kPage + (key % kPage)) * dm.hd) * esz;
+          bulk_load_1d(dst + (size_t)(isv ? c.npre_max : 0) * row + (size_t)r * row, (isv ? vb : kb) + off, row, bar);
+        }
+        if (lane == 31) {
+          const int t = d.is_global ? 1 : 0;
+          unsigned char* rp = dst + (size_t)2 * c.npre_max * row;
+          bulk_load_1d(rp, a.rope_cos[t] + (size_t)pos * (dm.hd / 2), rope_row, bar);
+          bulk_load_1d(rp + rope_row, a.rope_sin[t] + (size_t)pos * (dm.hd / 2), rope_row, bar);
+        }
+      }
+    } else {
+      const PhasePlan& p = c.plan[cur.ph];
+      if (p.work && cur.round < p.rounds) {
+        const LayerWeights& L = c.lw[cur.ph == kSH ? last : cur.layer];
+        const uint4* w;
+        const float* wscale;
+        const float *g_post = nullptr, *g_pre = nullptr;
+        switch (cur.ph) {
+          case kSA: w = L.wqkv; wscale = L.sqkv; g_pre = L.g_pre_attn;
+                    g_post = cur.layer > 0 ? c.lw[cur.layer - 1].g_post_ffn : nullptr; break;
+          case kSC: w = L.wo; wscale = L.so; break;
+          case kSD: w = L.wgu; wscale = L.sgu; g_pre = L.g_pre_ffn; g_post = L.g_post_attn; break;
+          case kSE: w = L.wdown; wscale = L.sdown; break;
+          default: w = a.head_w; wscale = a.embed_scale; g_pre = a.g_final; g_post = L.g_post_ffn; break;
+        }
+        d.valid = 1;
+        d.ktn = p.ktn;
+        d.ta = p.t0 + cur.round * p.tpr;
+        d.ntile = min(p.tpr, p.t1 - d.ta);
+        d.has_gains = (p.has_gains && cur.round == 0) ? 1 : 0;
+        if (lane == 0) c.slot[h] = d;
+        __syncwarp();
+        const int KT = p.K / 64, kt0 = p.slice * p.ktn;
+        const uint32_t tile_bytes = (uint32_t)p.ktn * 512u;
+        const uint32_t wbytes = (uint32_t)d.ntile * tile_bytes;
+        const uint32_t sbytes = (uint32_t)d.ntile * 64u;
+        const uint32_t gbytes = (uint32_t)dm.d * 4u;
+        uint32_t total = wbytes + sbytes + (d.has_gains ? (g_post ? 2u : 1u) * gbytes : 0u);
+        if (lane == 0) mbar_arrive_expect_tx(bar, total);
+        __syncwarp();
+        if (p.slices == 1) {
+          // one contiguous run of ntile * KT tiles, cut into 8 KiB pieces over the lanes
+          const unsigned char* src = reinterpret_cast<const unsigned char*>(w + (size_t)d.ta * KT * 32);
+          const uint32_t piece = 8192u;
+          const uint32_t npieces = (wbytes + piece - 1) / piece;
+          for (uint32_t i = lane; i < npieces; i += 32) {
+            uint32_t o = i * piece, nb = min(piece, wbytes - o);
+            bulk_load_1d(dst + o, src + o, nb, bar);
+          }
+        } else {
+          for (int i = lane; i < d.ntile; i += 32) {
+            const unsigned char* src = reinterpret_cast<const unsigned char*>(w + ((size_t)(d.ta + i) * KT + kt0) * 32);
+            bulk_load_1d(dst + (size_t)i * tile_bytes, src, tile_bytes, bar);
+          }
+        }
+        if (lane == 31) bulk_load_1d(dst + wbytes, wscale + (size_t)d.ta * 16, sbytes, bar);
+        if (d.has_gains) {
+          if (lane == 30) bulk_load_1d(dst + wbytes + sbytes, g_pre, gbytes, bar);
+          if (lane == 29 && g_post) bulk_load_1d(dst + wbytes + sbytes + gbytes, g_post, gbytes, bar);
+        }
+      }
+    }
+    if (!d.valid) {
+      if (lane == 0) {
+        c.slot[h] = d;
+        mbar_arrive(bar);      // an empty fill still completes its barrier phase
+      }
+      __syncwarp();
+    }
+    stream_advance(cur, c, dm.n_layers);
+  }
+}
+
+// ------------------------------------------------------------ consumer side
+
+__device__ __forceinline__ const FillDesc* stream_acquire(StreamCtx& c, unsigned char** hb, int* err) {
+  const unsigned n = c.wait_no, h = n & 1u;
+  mbar_wait(&c.full[h], (n >> 1) & 1u, err);
+  *hb = c.half[h];
+  return &c.slot[h];
+}
+// All compute threads are done with the half of the current fill.
+__device__ __forceinline__ void stream_release(StreamCtx& c) {
+  const unsigned h = c.wait_no & 1u;
+  ++c.wait_no;
+  dec_sync();
+  if (threadIdx.x == 0) mbar_arrive(&c.empty[h]);
+}
+
+// tiles in shared memory: tile u at wsm + u * ktn * 32 (uint4 units)
+__device__ __forceinline__ void gemv_tiles_smem(const uint4* wsm, int ktn, int nu, QuantCols xc, int* red) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int g = lane >> 2, t = lane & 3;
+  const int total = nu * ktn;
+  const int per = (total + kDecWarps - 1) / kDecWarps;
+  const int beg = warp * per;
+  const int end = min(total, beg + per);
+  const bool colok = g < xc.nq;
+  const int8_t* xrow = xc.q + (size_t)g * xc.stride + 4 * t;
+  int acc[4] = {0, 0, 0, 0};
+  int cur = -1;
+#pragma unroll 2
+  for (int b = beg; b < end; ++b) {
+    int un = b / ktn, kt = b - un * ktn;
+    uint4 w = wsm[(size_t)b * 32 + lane];
+    if (un != cur) {
+      if (cur >= 0) flush_tile(red, cur, acc, lane, xc.nq);
+      cur = un;
+      acc[0] = acc[1] = acc[2] = acc[3] = 0;
+    }
+    uint32_t b0 = 0, b1 = 0, b2 = 0, b3 = 0;
+    if (colok) {
+      const int8_t* xp = xrow + kt * 64;
+      b0 = *reinterpret_cast<const uint32_t*>(xp);
+      b1 = *reinterpret_cast<const uint32_t*>(xp + 16);
+      b2 = *reinterpret_cast<const uint32_t*>(xp + 32);
+      b3 = *reinterpret_cast<const uint32_t*>(xp + 48);
+    }
+    mma_tile_words(acc, w, b0, b1, b2, b3);
+  }
+  if (cur >= 0) flush_tile(red, cur, acc, lane, xc.nq);
+}
+
+// Four sums in one block reduction.
+__device__ __forceinline__ void block_sum4(float (&v)[4], float* scratch) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) v[k] = warp_sum(v[k]);
+  dec_sync();
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k) scratch[k * kDecWarps + (threadIdx.x >> 5)] = v[k];
+  }
+  dec_sync();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < kDecWarps; ++i) s += scratch[k * kDecWarps + i];
+    v[k] = s;
+  }
+}
+
+// Quantises four consecutive values (already divided by the scale) and stores each term as one word.
+__device__ __forceinline__ void quantize4(float4 r, int nterms, int8_t* q0, int stride) {
+  float v[4] = {r.x, r.y, r.z, r.w};
+  uint32_t w0 = 0, w1 = 0, w2 = 0;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    float t0 = fminf(fmaxf(rintf(v[k]), -127.f), 127.f);
+    w0 |= ((uint32_t)(int)t0 & 0xFFu) << (8 * k);
+    float r1 = (v[k] - t0) * 128.0f;
+    float t1 = fminf(fmaxf(rintf(r1), -127.f), 127.f);
+    w1 |= ((uint32_t)(int)t1 & 0xFFu) << (8 * k);
+    float r2 = (r1 - t1) * 128.0f;
+    float t2 = fminf(fmaxf(rintf(r2), -127.f), 127.f);
+    w2 |= ((uint32_t)(int)t2 & 0xFFu) << (8 * k);
+  }
+  *reinterpret_cast<uint32_t*>(q0) = w0;
+  if (nterms > 1) *reinterpret_cast<uint32_t*>(q0 + stride) = w1;
+  if (nterms > 2) *reinterpret_cast<uint32_t*>(q0 + 2 * stride) = w2;
+}
+
+// x = xin + rmsnorm(sum parts) * g_post ; xout <- x (cta 0) ; xq <- quantised rmsnorm(x) * g_pre.
+// One pass over L2 (16-byte loads held in registers), one block reduction.
+__device__ __forceinline__ void stream_prologue_resid(const DecodeArgs& a, StreamCtx& c, int cta, const float* parts,
+                                                      int nparts, const float* xin, float* xout, const float* g_post,
+                                                      const float* g_pre, float gmax_pre) {
+  const int d = a.dims.d, d4 = d / 4;
+  const DecodeSmem& s = c.s;
+  const float bound = sqrtf((float)d) * gmax_pre * 1.0001f;     // |rmsnorm(x)_i g_i| never exceeds it
+  const float inv = bound > 0.f ? 127.0f / bound : 0.f;
+  for (int col = 0; col < a.ncols; ++col) {
+    float4 f[kMaxV4], xi[kMaxV4], gp[kMaxV4];
+    float sums[4] = {0.f, 0.f, 0.f, 0.f};    // f^2, xin^2, xin f g_post, (f g_post)^2
+#pragma unroll
+    for (int u = 0; u < kMaxV4; ++u) {
+      const int i = threadIdx.x + u * kDecThreads;
+      f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+      xi[u] = f[u];
+      gp[u] = f[u];
+      if (i < d4) {
+        for (int p = 0; p < nparts; ++p) {
+          float4 v = __ldcg(reinterpret_cast<const float4*>(parts + ((size_t)p * a.ncols + col) * d) + i);
+          f[u].x += v.x; f[u].y += v.y; f[u].z += v.z; f[u].w += v.w;
+        }
+        xi[u] = __ldcg(reinterpret_cast<const float4*>(xin + (size_t)col * d) + i);
+        gp[u] = reinterpret_cast<const float4*>(g_post)[i];
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kMaxV4; ++u) {
+      float4 fg = make_float4(f[u].x * gp[u].x, f[u].y * gp[u].y, f[u].z * gp[u].z, f[u].w * gp[u].w);
+      sums[0] += f[u].x * f[u].x + f[u].y * f[u].y + f[u].z * f[u].z + f[u].w * f[u].w;
+      sums[1] += xi[u].x * xi[u].x + xi[u].y * xi[u].y + xi[u].z * xi[u].z + xi[u].w * xi[u].w;
+      sums[2] += xi[u].x * fg.x + xi[u].y * fg.y + xi[u].z * fg.z + xi[u].w * fg.w;
+      sums[3] += fg.x * fg.x + fg.y * fg.y + fg.z * fg.z + fg.w * fg.w;
+      gp[u] = fg;
+    }
+    block_sum4(sums, s.scratch);
+    const float r = rsqrtf(sums[0] / (float)d + a.dims.eps);
+    const float ss2 = fmaxf(sums[1] + 2.0f * r * sums[2] + r * r * sums[3], 0.f);
+    const float r2 = rsqrtf(ss2 / (float)d + a.dims.eps);
+    int8_t* q0 = s.xq + (size_t)(col * a.nterms) * s.xstride;
+#pragma unroll
+    for (int u = 0; u < kMaxV4; ++u) {
+      const int i = threadIdx.x + u * kDecThreads;
+      if (i < d4) {
+        float4 x = make_float4(xi[u].x + r * gp[u].x, xi[u].y + r * gp[u].y, xi[u].z + r * gp[u].z, xi[u].w + r * gp[u].w);
+        if (cta == 0) reinterpret_cast<float4*>(xout + (size_t)col * d)[i] = x;
+        float4 gq = reinterpret_cast<const float4*>(g_pre)[i];
+        const float k = r2 * inv;
+        quantize4(make_float4(x.x * gq.x * k, x.y * gq.y * k, x.z * gq.z * k, x.w * gq.w * k), a.nterms, q0 + 4 * i, s.xstride);
+      }
+    }
+    if (threadIdx.x == 0) s.colscale[col] = bound / 127.0f;
+  }
+  dec_sync();
+}
+
+__device__ __forceinline__ void stream_prologue_embed(const DecodeArgs& a, StreamCtx& c, int cta, float* xout,
+                                                      const float* g_pre, float gmax_pre) {
+  const int d = a.dims.d;
+  const DecodeSmem& s = c.s;
+  const float emb = sqrtf((float)d);
+  const float bound = sqrtf((float)d) * gmax_pre * 1.0001f;
+  const float inv = bound > 0.f ? 127.0f / bound : 0.f;
+  for (int col = 0; col < a.ncols; ++col) {
+    int tok = __ldcg(&a.st->token[col]);
+    if (tok < 0 || tok >= a.dims.vocab) {
+      if (threadIdx.x == 0) atomicExch(&a.st->err, (int)kDevBadToken);
+      tok = 0;
+    }
+    const uint8_t* row = a.embed_rows + (size_t)tok * (d / 2);
+    const float sc = a.embed_scale[tok] * emb;
+    float* x = s.xf + (size_t)col * d;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < d; i += kDecThreads) {
+      int b = row[i >> 1];
+      int nib = (i & 1) ? (b >> 4) : (b & 0xF);
+      float v = (float)(nib >= 8 ? nib - 16 : nib) * sc;
+      x[i] = v;
+      ss += v * v;
+      if (cta == 0) xout[(size_t)col * d + i] = v;
+    }
+    ss = block_sum(ss, s.scratch);
+    const float k = rsqrtf(ss / (float)d + a.dims.eps) * inv;
+    int8_t* q0 = s.xq + (size_t)(col * a.nterms) * s.xstride;
+    for (int i = threadIdx.x; i < d; i += kDecThreads) quantize_value(x[i] * g_pre[i] * k, a.nterms, q0 + i, s.xstride);
+    if (threadIdx.x == 0) s.colscale[col] = bound / 127.0f;
+  }
+  dec_sync();
+}
+
+// ---------------------------------------------------------------- attention
+// One (query, kv head, split) item with its K/V rows staged in shared memory.
+// Scores: one thread per (head, key) walks the row in a lane-rotated order, so
+// the 32 rows a warp touches fall into different banks.  One softmax per CTA
+// per chunk (no per-warp partial states), then one thread per output element
+// accumulates P.V.  Splits longer than the staging half are processed in
+// chunks with an online softmax; chunks that were not prefetched are fetched
+// synchronously (compute warp 0 issues, everybody waits on the aux barrier).
+template <typename T>
+__device__ __forceinline__ float4 load4_smem(const T* p) {
+  if constexpr (sizeof(T) == 4) {
+    return *reinterpret_cast<const float4*>(p);
+  } else {
+    uint2 v = *reinterpret_cast<const uint2*>(p);
+    __nv_bfloat162 x = *reinterpret_cast<__nv_bfloat162*>(&v.x);
+    __nv_bfloat162 y = *reinterpret_cast<__nv_bfloat162*>(&v.y);
+    return make_float4(__low2float(x), __high2float(x), __low2float(y), __high2float(y));
+  }
+}
+
+struct AttnItem {
+  int layer, col, kvh, split, nsplit, is_global;
+  int nstaged;              // rows of chunk 0 already in the half (prefetched), else -1
+  const float *cos_r, *sin_r;   // RoPE row of the query position (shared or global memory)
+};
+
+template <typename T, int HD, int G>
+__device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c, const AttnItem& it, unsigned char* hb) {
+  const ModelDims& dm = a.dims;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  constexpr int half = HD / 2, C4 = HD / 4;
+  const int qi = it.col, kvh = it.kvh;
+  const LayerWeights& L = c.lw[it.layer];
+  const LayerKv kv = c.lkv[it.layer];
+  int pos = __ldcg(&a.st->pos[qi]);
+  if (pos < 0 || pos >= dm.max_ctx) {
+    if (threadIdx.x == 0) atomicExch(&a.st->err, (int)kDevBadPosition);
+    pos = 0;
+  }
+  const int cap = c.npre_max;
+  float* q_s = c.s.attn;               // [G][HD]
+  float* k_s = q_s + G * HD;           // [HD] new key (normed, roped)
+  float* v_s = k_s + HD;               // [HD]
+  float* sc = v_s + HD;                // [G][cap + 1] scores, then probabilities
+  float* st = sc + G * (cap + 1);      // [G][4]: m, l, corr
+  const size_t rowb = (size_t)HD * sizeof(T);
+  const T* kpre = reinterpret_cast<const T*>(hb);
+  const T* vpre = reinterpret_cast<const T*>(hb + (size_t)cap * rowb);
+  const float* row = a.qkv + (size_t)qi * dm.nqkv();
+  const float att_scale = rsqrtf((float)HD);
+  // ---- stage q heads, the new key and value
+  for (int h = warp; h < G + 2; h += kDecWarps) {
+    if (h <= G) {
+      const float* src = h < G ? row + (size_t)(kvh * G + h) * HD : row + dm.nq() + (size_t)kvh * HD;
+      const float* gain = h < G ? L.g_q : L.g_k;
+      float* dst = h < G ? q_s + h * HD : k_s;
+      float v[HD / 32];
+      float ss = 0.f;
+#pragma unroll
+      for (int i = 0; i < HD / 32; ++i) { v[i] = __ldcg(src + lane + 32 * i); ss += v[i] * v[i]; }
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / (float)HD + dm.eps);
+      const float post = h < G ? att_scale : 1.0f;
+      if constexpr (HD == 32) {                 // the pair of element e sits 16 lanes away
+        float x = v[0] * r * gain[lane];
+        float y = __shfl_xor_sync(0xffffffffu, x, 16);
+        if (lane < 16) {
+          float cs = it.cos_r[lane], sn = it.sin_r[lane];
+          dst[lane] = (x * cs - y * sn) * post;
+          dst[lane + 16] = (y * cs + x * sn) * post;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < HD / 64; ++i) {     // element e = lane + 32 i pairs with e + half
+          const int e = lane + 32 * i;
+          float a0 = v[i] * r * gain[e], b0 = v[i + HD / 64] * r * gain[e + half];
+          float cs = it.cos_r[e], sn = it.sin_r[e];
+          dst[e] = (a0 * cs - b0 * sn) * post;
+          dst[e + half] = (b0 * cs + a0 * sn) * post;
+        }
+      }
+    } else {
+      const float* src = row + dm.nq() + dm.nkv() + (size_t)kvh * HD;
+#pragma unroll
+      for (int i = 0; i < HD / 32; ++i) v_s[lane + 32 * i] = __ldcg(src + lane + 32 * i);
+    }
+  }
+  if (threadIdx.x < G) { st[threadIdx.x * 4] = -INFINITY; st[threadIdx.x * 4 + 1] = 0.f; st[threadIdx.x * 4 + 2] = 1.f; }
+  dec_sync();
+  const int* ptab = a.page_table + (size_t)qi * a.pages_per_seq;
+  if (it.split == 0) {     // KV append: exactly one CTA per (query, kv head)
+    T* kbase = reinterpret_cast<T*>(kv.k);
+    T* vbase = reinterpret_cast<T*>(kv.v);
+    size_t off = (((size_t)ptab[pos / kPage] * dm.hkv + kvh) * kPage + (pos % kPage)) * HD;
+    for (int e = threadIdx.x; e < HD; e += kDecThreads) {
+      if constexpr (sizeof(T) == 4) {
+        kbase[off + e] = k_s[e];
+        vbase[off + e] = v_s[e];
+        if (kv.k16) { kv.k16[off + e] = __float2bfloat16(k_s[e]); kv.v16[off + e] = __float2bfloat16(v_s[e]); }
+      } else {
+        kbase[off + e] = __float2bfloat16(k_s[e]);
+        vbase[off + e] = __float2bfloat16(v_s[e]);
+      }
+    }
+  }
+  int k0, k1;
+  attn_split_range(dm, pos, it.is_global, it.nsplit, it.split, &k0, &k1);
+  const bool has_new = k1 == pos + 1 && k1 > k0;      // this split ends with the new key
+  const int n_old = (has_new ? k1 - 1 : k1) - k0;     // rows that live in the cache
+  if constexpr (sizeof(T) == 2) {                     // what a bf16 cache would hand back
+    for (int e = threadIdx.x; e < HD; e += kDecThreads) {
+      k_s[e] = __bfloat162float(__float2bfloat16(k_s[e]));
+      v_s[e] = __bfloat162float(__float2bfloat16(v_s[e]));
+    }
+    dec_sync();
+  }
+  float o0 = 0.f, o1 = 0.f;     // outputs idx = threadIdx.x and threadIdx.x + kDecThreads of [G][HD]
+  const int nchunks = n_old <= 0 ? 1 : (n_old + cap - 1) / cap;
+  for (int ch = 0; ch < nchunks; ++ch) {
+    const int c0 = ch * cap;
+    const int nrows = max(0, min(cap, n_old - c0));
+    const bool staged = ch == 0 && it.nstaged >= nrows;
+    if (!staged && nrows > 0) {       // fetch these rows into the half now
+      dec_sync();
+      if (threadIdx.x < 32) {
+        if (lane == 0) mbar_arrive_expect_tx(c.aux, 2u * (uint32_t)nrows * (uint32_t)rowb);
+        __syncwarp();
+        const unsigned char* kb = reinterpret_cast<const unsigned char*>(kv.k);
+        const unsigned char* vb = reinterpret_cast<const unsigned char*>(kv.v);
+        for (int i = lane; i < 2 * nrows; i += 32) {
+          int r = i >> 1, isv = i & 1, key = k0 + c0 + r;
+          size_t off = ((((size_t)ptab[key / kPage] * dm.hkv + kvh) * kPage + (key % kPage)) * HD) * sizeof(T);
+          bulk_load_1d(hb + (size_t)(isv ? cap : 0) * rowb + (size_t)r * rowb, (isv ? vb : kb) + off, (uint32_t)rowb, c.aux);
+        }
+      }
+      unsigned par = c.aux_cnt & 1u;
+      ++c.aux_cnt;
+      mbar_wait(c.aux, par, &a.st->err);
+    }
+    const bool lastc = ch == nchunks - 1;
+    const int nk = nrows + ((lastc && has_new) ? 1 : 0);
+    // ---- scores
+    for (int p = threadIdx.x; p < G * nk; p += kDecThreads) {
+      const int g = p / nk, kk = p - g * nk;
+      const float* qrow = q_s + g * HD;
+      float acc = 0.f;
+      if (kk < nrows) {
+        const T* kr = kpre + (size_t)kk * HD;
+#pragma unroll 4
+        for (int i = 0; i < C4; ++i) {
+          const int cc = (i + lane) & (C4 - 1);
+          float4 kx = load4_smem<T>(kr + 4 * cc);
+          float4 qv = *reinterpret_cast<const float4*>(qrow + 4 * cc);
+          acc += kx.x * qv.x + kx.y * qv.y + kx.z * qv.z + kx.w * qv.w;
+        }
+      } else {
+#pragma unroll 4
+        for (int i = 0; i < C4; ++i) {
+          const int cc = (i + lane) & (C4 - 1);
+          float4 kx = *reinterpret_cast<const float4*>(k_s + 4 * cc);
+          float4 qv = *reinterpret_cast<const float4*>(qrow + 4 * cc);
+          acc += kx.x * qv.x + kx.y * qv.y + kx.z * qv.z + kx.w * qv.w;
+        }
+      }
+      sc[g * (cap + 1) + kk] = acc;
+    }
+    dec_sync();
+    // ---- softmax statistics of this chunk, merged into the running (m, l)
+    if (warp < G) {
+      float* sg = sc + warp * (cap + 1);
+      float mc = -INFINITY;
+      for (int kk = lane; kk < nk; kk += 32) mc = fmaxf(mc, sg[kk]);
+      mc = warp_max(mc);
+      const float m_old = st[warp * 4], l_old = st[warp * 4 + 1];
+      const float m_new = fmaxf(m_old, mc);
+      float lc = 0.f;
+      for (int kk = lane; kk < nk; kk += 32) {
+        float pv = __expf(sg[kk] - m_new);
+        sg[kk] = pv;
+        lc += pv;
+      }
+      lc = warp_sum(lc);
+      if (lane == 0) {
+        const float corr = m_new == -INFINITY ? 1.0f : __expf(m_old - m_new);
+        st[warp * 4] = m_new;
+        st[warp * 4 + 1] = l_old * corr + lc;
+        st[warp * 4 + 2] = corr;
+      }
+    }
+    dec_sync();
+    // ---- P.V for the outputs this thread owns
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+      const int idx = threadIdx.x + u * kDecThreads;
+      if (idx < G * HD) {
+        const int g = idx / HD, e = idx - g * HD;
+        const float* sg = sc + g * (cap + 1);
+        float acc = (u == 0 ? o0 : o1) * st[g * 4 + 2];
+        int kk = 0;
+        for (; kk + 4 <= nrows; kk += 4) {
+          float v0 = kv_to_float<T>(vpre[(size_t)kk * HD + e]), v1 = kv_to_float<T>(vpre[(size_t)(kk + 1) * HD + e]);
+          float v2 = kv_to_float<T>(vpre[(size_t)(kk + 2) * HD + e]), v3 = kv_to_float<T>(vpre[(size_t)(kk + 3) * HD + e]);
+          acc += sg[kk] * v0 + sg[kk + 1] * v1 + sg[kk + 2] * v2 + sg[kk + 3] * v3;
+        }
+        for (; kk < nrows; ++kk) acc += sg[kk] * kv_to_float<T>(vpre[(size_t)kk * HD + e]);
+        if (nk > nrows) acc += sg[nrows] * v_s[e];
+        if (u == 0) o0 = acc; else o1 = acc;
+      }
+    }
+  }
+  // ---- partial result of this split: (m, l, unnormalised o)
+  static_assert(G * HD <= 2 * kDecThreads, "two outputs per thread cover the group");
+#pragma unroll
+  for (int u = 0; u < 2; ++u) {
+    const int idx = threadIdx.x + u * kDecThreads;
+    if (idx < G * HD) {
+      const int g = idx / HD, e = idx - g * HD;
+      size_t pi = (((size_t)qi * dm.hkv + kvh) * it.nsplit + it.split) * G + g;
+      a.part_o[pi * HD + e] = u == 0 ? o0 : o1;
+      if (e == 0) { a.part_ml[pi * 2] = st[g * 4]; a.part_ml[pi * 2 + 1] = st[g * 4 + 1]; }
+    }
+  }
+  dec_sync();
+}
+
+template <typename T, int HD>
+__device__ __forceinline__ void attn_smem_g(const DecodeArgs& a, StreamCtx& c, const AttnItem& it, unsigned char* hb) {
+  switch (a.dims.hq / a.dims.hkv) {
+    case 1: attn_smem_item<T, HD, 1>(a, c, it, hb); break;
+    case 2: attn_smem_item<T, HD, 2>(a, c, it, hb); break;
+    default: attn_smem_item<T, HD, 4>(a, c, it, hb); break;
+  }
+}
+__device__ __forceinline__ void attn_smem_dispatch(const DecodeArgs& a, StreamCtx& c, const AttnItem& it, unsigned char* hb) {
+  if (a.dims.kv_dtype == 0) {
+    switch (a.dims.hd) {
+      case 32: attn_smem_g<float, 32>(a, c, it, hb); break;
+      case 64: attn_smem_g<float, 64>(a, c, it, hb); break;
+      case 128: attn_smem_g<float, 128>(a, c, it, hb); break;
+      default: attn_smem_g<float, 256>(a, c, it, hb); break;
+    }
+  } else {
+    switch (a.dims.hd) {
+      case 32: attn_smem_g<__nv_bfloat16, 32>(a, c, it, hb); break;
+      case 64: attn_smem_g<__nv_bfloat16, 64>(a, c, it, hb); break;
+      case 128: attn_smem_g<__nv_bfloat16, 128>(a, c, it, hb); break;
+      default: attn_smem_g<__nv_bfloat16, 256>(a, c, it, hb); break;
+    }
+  }
+}
+
+// Log-sum-exp combine of the split partials of one head slice into xf (then quantised).
+// All loads of a thread are independent, so they overlap.
+__device__ __forceinline__ void stream_prologue_combine(const DecodeArgs& a, StreamCtx& c, int layer) {
+  const ModelDims& dm = a.dims;
+  const PhasePlan& p = c.plan[kSC];
+  const int Ks = dm.nq() / a.o_slices, hps = Ks / dm.hd, G = dm.group();
+  const int nsplit = c.lw[layer].is_global ? a.n_attn_splits_global : a.n_attn_splits_local;
+  float* mls = c.s.argbuf;                       // [hps][nsplit][2]
+  float* wts = c.s.argbuf + kDecThreads;         // [hps][nsplit] normalised weights
+  for (int col = 0; col < a.ncols; ++col) {
+    if (col > 0) dec_sync();
+    for (int i = threadIdx.x; i < hps * nsplit * 2; i += kDecThreads) {
+      int hh = i / (nsplit * 2), rem = i - hh * nsplit * 2, sp = rem >> 1, w = rem & 1;
+      int h = p.slice * hps + hh, kvh = h / G, g = h % G;
+      size_t pi = (((size_t)col * dm.hkv + kvh) * nsplit + sp) * G + g;
+      mls[i] = __ldcg(a.part_ml + pi * 2 + w);
+    }
+    dec_sync();
+    for (int hh = threadIdx.x >> 5; hh < hps; hh += kDecWarps) {
+      const int lane = threadIdx.x & 31;
+      const float* ml = mls + (size_t)hh * nsplit * 2;
+      float M = -INFINITY;
+      for (int sp = lane; sp < nsplit; sp += 32) M = fmaxf(M, ml[sp * 2]);
+      M = warp_max(M);
+      float Lsum = 0.f;
+      for (int sp = lane; sp < nsplit; sp += 32) Lsum += ml[sp * 2 + 1] * __expf(ml[sp * 2] - M);
+      Lsum = warp_sum(Lsum);
+      const float invL = Lsum > 0.f ? 1.0f / Lsum : 0.f;
+      for (int sp = lane; sp < nsplit; sp += 32) wts[hh * nsplit + sp] = __expf(ml[sp * 2] - M) * invL;
+    }
+    dec_sync();
+    for (int i = threadIdx.x; i < Ks; i += kDecThreads) {
+      int hh = i / dm.hd, e = i - hh * dm.hd;
+      int h = p.slice * hps + hh, kvh = h / G, g = h % G;
+      const float* po = a.part_o + ((((size_t)col * dm.hkv + kvh) * nsplit) * G + g) * dm.hd + e;
+      const size_t stride = (size_t)G * dm.hd;
+      const float* w = wts + hh * nsplit;
+      float acc = 0.f;
+      int sp = 0;
+      for (; sp + 16 <= nsplit; sp += 16) {
+        float v[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) v[u] = __ldcg(po + (size_t)(sp + u) * stride);
+#pragma unroll
+        for (int u = 0; u < 16; ++u) acc += v[u] * w[sp + u];
+      }
+      for (; sp < nsplit; ++sp) acc += __ldcg(po + (size_t)sp * stride) * w[sp];
+      c.s.xf[(size_t)col * Ks + i] = acc;
+    }
+  }
+  dec_sync();
+  quantize_cols(c.s, Ks, a.ncols, a.nterms);
+}
+
+// One GEMV phase of the stream: for every round acquire / (prologue) / MMA / epilogue / release.
+template <typename Prologue>
+__device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx& c, int ph, float* y, Prologue prologue,
+                                                  float* best_val, int* best_idx, int bar) {
+  const PhasePlan& p = c.plan[ph];
+  const int ncols = a.ncols, nterms = a.nterms;
+  const int fills = p.rounds > 1 ? p.rounds : 1;
+  for (int r = 0; r < fills; ++r) {
+    unsigned char* hb;
+    if (r == 0) B2_TP(0);
+    const FillDesc* fd = stream_acquire(c, &hb, &a.st->err);
+    if (r == 0) B2_TP(1);
+    if (fd->ph != ph && threadIdx.x == 0) atomicExch(&a.st->err, (int)kDevBarrierTimeout);   // sequence out of step
+    if (fd->valid && fd->ph == ph) {
+      const int ntile = fd->ntile, ktn = fd->ktn, ta = fd->ta;
+      const uint4* wsm = reinterpret_cast<const uint4*>(hb);
+      const float* ssm = reinterpret_cast<const float*>(hb + (size_t)ntile * ktn * 512);
+      const float* gsm = ssm + ntile * 16;          // g_pre then g_post (round 0 of norm phases)
+      if (r == 0) prologue(gsm, gsm + a.dims.d);
+      if (r == 0) B2_TP(3);
+      QuantCols xc{c.s.xq, c.s.xstride, ncols * nterms};
+      gemv_tiles_smem(wsm, ktn, ntile, xc, c.s.red);
+      dec_sync();
+      if (r == 0) B2_TP(4);
+      if (p.epilogue == kEpiGeglu) {
+        const int npair = ntile / 2;
+        for (int i = threadIdx.x; i < npair * 16 * ncols; i += kDecThreads) {
+          int col = i / (npair * 16), rem = i - col * npair * 16;
+          int pr = rem / 16, row = rem & 15;
+          float gate = finalize_value(c.s, 2 * pr, row, col, nterms) * ssm[(2 * pr) * 16 + row];
+          float up = finalize_value(c.s, 2 * pr + 1, row, col, nterms) * ssm[(2 * pr + 1) * 16 + row];
+          y[(size_t)col * (p.N / 2) + (size_t)(ta / 2 + pr) * 16 + row] = gelu_tanh(gate) * up;
+          for (int t = 0; t < nterms; ++t) {           // leave the accumulators clean for the next round
+            c.s.red[((2 * pr) * 16 + row) * kQCols + col * nterms + t] = 0;
+            c.s.red[((2 * pr + 1) * 16 + row) * kQCols + col * nterms + t] = 0;
+          }
+        }
+      } else {
+        for (int i = threadIdx.x; i < ntile * 16 * ncols; i += kDecThreads) {
+          int col = i / (ntile * 16), rem = i - col * ntile * 16;
+          int un = rem / 16, row = rem & 15;
+          int n = (ta + un) * 16 + row;
+          float v = finalize_value(c.s, un, row, col, nterms) * ssm[un * 16 + row];
+          y[((size_t)p.slice * ncols + col) * p.N + n] = v;
+          for (int t = 0; t < nterms; ++t) c.s.red[(un * 16 + row) * kQCols + col * nterms + t] = 0;
+          if (p.epilogue == kEpiHead && col < kMaxCols) {
+            if (v > best_val[col] || (v == best_val[col] && n < best_idx[col])) { best_val[col] = v; best_idx[col] = n; }
+          }
+        }
+      }
+    }
+    stream_release(c);
+    if (r == 0) B2_TP(5);
+  }
+  B2_TP(6);
+}
+
+__global__ void __launch_bounds__(kStreamThreads, 1)
+decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned int epoch0, int half_bytes) {
+  extern __shared__ __align__(128) unsigned char ssm_raw[];
+  __shared__ unsigned int epoch;
+  StreamCtx c;
+  stream_carve(ssm_raw, a.dims, a.ncols, half_bytes, c);
+  const int cta = blockIdx.x, ncta = gridDim.x;
+  const ModelDims& dm = a.dims;
+  if (threadIdx.x == 0) {
+    epoch = epoch0;
+    for (int i = 0; i < 2; ++i) { mbar_init(&c.full[i], 1); mbar_init(&c.empty[i], 1); }
+    mbar_init(c.aux, 1);
+    *c.step_ready = 1;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  for (int i = threadIdx.x; i < dm.n_layers; i += kStreamThreads) {
+    c.lw[i] = a.layers[i];
+    c.lkv[i] = a.kv[i];
+  }
+  for (int i = threadIdx.x; i < kMaxRoundUnits * 16 * kQCols; i += kStreamThreads) c.s.red[i] = 0;
+  const int esz_kv = dm.kv_dtype == 0 ? 4 : 2;
+  c.npre_max = min(kStreamMaxStagedRows, (half_bytes - dm.hd * 4) / (2 * dm.hd * esz_kv));
+  c.wait_no = 0;
+  c.aux_cnt = 0;
+  __syncthreads();
+  if (threadIdx.x == 0) stream_make_plans(a, c, cta, ncta);
+  __syncthreads();
+
+  if (threadIdx.x >= kDecThreads) {       // ---- producer warp
+    stream_producer(a, c, cta, nsteps);
+    return;
+  }
+
+  int bar = 0;
+  for (int step = 0; step < nsteps; ++step) {
+    if (threadIdx.x == 0) *c.step_ready = step + 1;
+    for (int layer = 0; layer < dm.n_layers; ++layer) {
+      const LayerWeights& L = c.lw[layer];
+      // ---- A: residual + pre-attention norm -> QKV
+      if (layer == 0) {
+        stream_gemv_phase(a, c, kSA, a.qkv,
+                          [&](const float* g_pre, const float*) { stream_prologue_embed(a, c, cta, a.xres[1], g_pre, L.gmax_pre_attn); },
+                          nullptr, nullptr, bar);
+      } else {
+        stream_gemv_phase(a, c, kSA, a.qkv,
+                          [&](const float* g_pre, const float* g_post) {
+                            stream_prologue_resid(a, c, cta, a.fpart, a.down_slices, a.xres[0], a.xres[1], g_post, g_pre,
+                                                  L.gmax_pre_attn);
+                          },
+                          nullptr, nullptr, bar);
+      }
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
+      // ---- B: attention (K/V rows and the RoPE row staged by the producer)
+      {
+        unsigned char* hb;
+        B2_TP(0);
+        const FillDesc* fd = stream_acquire(c, &hb, &a.st->err);
+        B2_TP(1);
+        if (fd->ph != kSB && threadIdx.x == 0) atomicExch(&a.st->err, (int)kDevBarrierTimeout);
+        const int is_global = L.is_global;
+        const int nsplit = is_global ? a.n_attn_splits_global : a.n_attn_splits_local;
+        const int items = a.ncols * dm.hkv * nsplit;
+        const size_t rowb = (size_t)dm.hd * esz_kv;
+        for (int itx = cta; itx < items; itx += ncta) {
+          AttnItem it;
+          it.layer = layer;
+          it.split = itx % nsplit;
+          int rest = itx / nsplit;
+          it.kvh = rest % dm.hkv;
+          it.col = rest / dm.hkv;
+          it.nsplit = nsplit;
+          it.is_global = is_global;
+          if (itx == cta && fd->valid && fd->ph == kSB) {
+            it.nstaged = fd->npre;
+            it.cos_r = reinterpret_cast<const float*>(hb + (size_t)2 * c.npre_max * rowb);
+            it.sin_r = it.cos_r + dm.hd / 2;
+          } else {            // further items of this CTA: rows fetched on the spot
+            int pos = __ldcg(&a.st->pos[it.col]);
+            if (pos < 0 || pos >= dm.max_ctx) pos = 0;
+            it.nstaged = -1;
+            it.cos_r = a.rope_cos[is_global ? 1 : 0] + (size_t)pos * (dm.hd / 2);
+            it.sin_r = a.rope_sin[is_global ? 1 : 0] + (size_t)pos * (dm.hd / 2);
+          }
+          attn_smem_dispatch(a, c, it, hb);
+        }
+        B2_TP(4);
+        stream_release(c);
+      }
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
+      // ---- C: combine partials of one head slice -> O projection
+      stream_gemv_phase(a, c, kSC, a.opart, [&](const float*, const float*) { stream_prologue_combine(a, c, layer); },
+                        nullptr, nullptr, bar);
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
+      // ---- D: post-attention norm + residual + pre-FFN norm -> gate/up + GeGLU
+      stream_gemv_phase(a, c, kSD, a.act,
+                        [&](const float* g_pre, const float* g_post) {
+                          stream_prologue_resid(a, c, cta, a.opart, a.o_slices, a.xres[1], a.xres[0], g_post, g_pre,
+                                                L.gmax_pre_ffn);
+                        },
+                        nullptr, nullptr, bar);
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
+      // ---- E: activation slice -> down projection
+      stream_gemv_phase(a, c, kSE, a.fpart,
+                        [&](const float*, const float*) {
+                          const PhasePlan& p = c.plan[kSE];
+                          const int Ks = dm.ffn / a.down_slices;
+                          for (int col = 0; col < a.ncols; ++col)
+                            for (int i = threadIdx.x; i < Ks / 4; i += kDecThreads)
+                              reinterpret_cast<float4*>(c.s.xf + (size_t)col * Ks)[i] =
+                                  __ldcg(reinterpret_cast<const float4*>(a.act + (size_t)col * dm.ffn + (size_t)p.slice * Ks) + i);
+                          dec_sync();
+                          quantize_cols(c.s, Ks, a.ncols, a.nterms);
+                        },
+                        nullptr, nullptr, bar);
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
+    }
+    // ---- H: final residual + final norm -> LM head + arg-max
+    float bv[kMaxCols];
+    int bi[kMaxCols];
+#pragma unroll
+    for (int cc = 0; cc < kMaxCols; ++cc) { bv[cc] = -INFINITY; bi[cc] = 0x7fffffff; }
+    stream_gemv_phase(a, c, kSH, a.logits,
+                      [&](const float* g_pre, const float* g_post) {
+                        stream_prologue_resid(a, c, cta, a.fpart, a.down_slices, a.xres[0], a.xres[1], g_post, g_pre,
+                                              a.gmax_final);
+                      },
+                      bv, bi, bar);
+    {
+      float* sv = c.s.argbuf;
+      int* si = reinterpret_cast<int*>(c.s.argbuf + kDecThreads);
+      for (int col = 0; col < a.ncols; ++col) {
+        dec_sync();
+        sv[threadIdx.x] = bv[col];
+        si[threadIdx.x] = bi[col];
+        dec_sync();
+        for (int stp = kDecThreads / 2; stp > 0; stp >>= 1) {
+          if (threadIdx.x < stp) {
+            float ov = sv[threadIdx.x + stp];
+            int oi = si[threadIdx.x + stp];
+            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
+              sv[threadIdx.x] = ov;
+              si[threadIdx.x] = oi;
+            }
+          }
+          dec_sync();
+        }
+        if (threadIdx.x == 0) {
+          a.amax_val[(size_t)cta * a.ncols + col] = sv[0];
+          a.amax_idx[(size_t)cta * a.ncols + col] = si[0];
+        }
+      }
+    }
+    grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
+    if (cta == 0) phase_argmax(a, ncta);
+    grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
+  }
+}
+
+}  // namespace b200lm

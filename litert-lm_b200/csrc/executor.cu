@@ -7,6 +7,7 @@
 #include <stdlib.h>
 
 #include <algorithm>
+#include <cmath>
 #include <fstream>
 #include <memory>
 #include <string>
@@ -15,6 +16,7 @@
 #include "../../include/b200lm.h"
 #include "common.cuh"
 #include "decode_ops.cuh"
+#include "decode_stream.cuh"
 #include "model_host.h"
 #include "prefill_ops.cuh"
 #include "runtime.h"
@@ -87,6 +89,11 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
     m->head_w = upload_w4t(*m, bytes(e), d.vocab, d.d);
   }
   m->g_final = fvec("final_norm", d.d);
+  {
+    const float* g = reinterpret_cast<const float*>(bytes(rec.need("final_norm", 1)));
+    m->gmax_final = 0.f;
+    for (int k = 0; k < d.d; ++k) m->gmax_final = std::max(m->gmax_final, std::fabs(g[k]));
+  }
   m->layers_host.resize(d.n_layers);
   m->gemm_host.resize(d.n_layers);
   for (int i = 0; i < d.n_layers; ++i) {
@@ -131,6 +138,14 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
       }
       L.sgu = upload(*m, sc.data(), sc.size());
     }
+    auto gmax = [&](const std::string& nm) {
+      const float* g = reinterpret_cast<const float*>(bytes(rec.need(nm, 1)));
+      float m = 0.f;
+      for (int k = 0; k < d.d; ++k) m = std::max(m, std::fabs(g[k]));
+      return m;
+    };
+    L.gmax_pre_attn = gmax(p + "pre_attn");
+    L.gmax_pre_ffn = gmax(p + "pre_ffn");
     L.g_pre_attn = fvec(p + "pre_attn", d.d);
     L.g_post_attn = fvec(p + "post_attn", d.d);
     L.g_pre_ffn = fvec(p + "pre_ffn", d.d);
@@ -307,13 +322,20 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   a.dims = d;
   a.ncols = 1;
   a.nterms = 3;
-  a.n_attn_splits_local = std::max(1, std::min(32, d.window / 64));
-  a.n_attn_splits_global = std::max(1, std::min(32, d.max_ctx / 128));
+  // a split of 32 (local) / 64 (global, at full context) keys fits one staged chunk
+  a.n_attn_splits_local = std::max(1, std::min(kMaxSplits, d.window / 32));
+  a.n_attn_splits_global = std::max(1, std::min(kMaxSplits, d.max_ctx / 64));
   int hps = 1;
   while ((hps * d.hd) % 64 != 0) ++hps;
   B2_CHECK(d.hq % hps == 0, kUnimplemented, "q heads cannot be grouped into 64-wide slices");
   a.o_slices = d.hq / hps;
   while (a.o_slices > e->n_sms) a.o_slices /= 2;
+  {   // the combine of split partials stages (m, l) of one head slice in 512 floats
+    int heads_per_slice = d.hq / a.o_slices;
+    int cap = std::max(1, 256 / heads_per_slice);
+    a.n_attn_splits_local = std::min(a.n_attn_splits_local, cap);
+    a.n_attn_splits_global = std::min(a.n_attn_splits_global, cap);
+  }
   int KTd = d.ffn / 64;
   a.down_slices = 1;
   for (int s = 4; s >= 2; --s)
@@ -326,6 +348,7 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   a.embed_scale = model->embed_scale;
   a.head_w = model->head_w;
   a.g_final = model->g_final;
+  a.gmax_final = model->gmax_final;
   for (int t = 0; t < 2; ++t) { a.rope_cos[t] = model->rope_cos[t]; a.rope_sin[t] = model->rope_sin[t]; }
   a.st = reinterpret_cast<DecodeState*>(e->alloc(sizeof(DecodeState), true));
   const int G = d.group();
@@ -350,6 +373,22 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   B2_CUDA(cudaFuncSetAttribute(decode_phase_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->dec_smem));
   B2_CUDA(cudaFuncSetAttribute(decode_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->dec_smem));
   if (e->decode_mode == B200LM_DECODE_PERSISTENT) {
+    // staging halves take what shared memory the activation staging leaves, up to 96 KiB each
+    size_t fixed = stream_fixed_bytes(d, a.ncols);
+    long room = ((long)prop.sharedMemPerBlockOptin - (long)fixed) / 2;
+    int half = (int)std::min<long>(room, 96 * 1024) / 1024 * 1024;
+    bool ok = half > 0 && stream_model_fits(d, a.o_slices, a.down_slices, half) && prop.cooperativeLaunch;
+    if (ok) {
+      e->stream_half = half;
+      e->stream_smem = fixed + 2 * (size_t)half;
+      B2_CUDA(cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->stream_smem));
+      int occ = 0;
+      B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_stream_kernel, kStreamThreads, e->stream_smem));
+      ok = occ >= 1;
+    }
+    if (!ok) e->decode_mode = B200LM_DECODE_PHASE_KERNELS;
+  }
+  if (e->decode_mode == B200LM_DECODE_PERSISTENT_BASIC) {
     int occ = 0;
     B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_persistent_kernel, kDecThreads, e->dec_smem));
     if (occ < 1 || !prop.cooperativeLaunch) e->decode_mode = B200LM_DECODE_PHASE_KERNELS;
@@ -526,12 +565,19 @@ void Executor::prefill(const int* ids, int n, bool wait, const volatile int* can
 void Executor::launch_decode_steps(int nsteps) {
   const ModelDims& d = model->dims;
   const int ncta = n_sms;
-  if (decode_mode == B200LM_DECODE_PERSISTENT) {
+  if (decode_mode == B200LM_DECODE_PERSISTENT || decode_mode == B200LM_DECODE_PERSISTENT_BASIC) {
     DecodeArgs a = dargs;
     unsigned epoch0 = barrier_epoch;
-    void* params[] = {&a, &nsteps, &epoch0};
-    B2_CUDA(cudaLaunchCooperativeKernel((void*)decode_persistent_kernel, dim3(ncta), dim3(kDecThreads), params,
-                                        dec_smem, stream));
+    if (decode_mode == B200LM_DECODE_PERSISTENT) {
+      int half = stream_half;
+      void* params[] = {&a, &nsteps, &epoch0, &half};
+      B2_CUDA(cudaLaunchCooperativeKernel((void*)decode_stream_kernel, dim3(ncta), dim3(kStreamThreads), params,
+                                          stream_smem, stream));
+    } else {
+      void* params[] = {&a, &nsteps, &epoch0};
+      B2_CUDA(cudaLaunchCooperativeKernel((void*)decode_persistent_kernel, dim3(ncta), dim3(kDecThreads), params,
+                                          dec_smem, stream));
+    }
     barrier_epoch += (unsigned)nsteps * (unsigned)(5 * d.n_layers + 2) * (unsigned)ncta;
     launches += 1;
     return;
@@ -605,6 +651,37 @@ void Executor::decode_tokens(int nsteps, int* out_ids) {
     next_input_token = t;
   }
   current_step += nsteps;
+}
+
+void Executor::trace_decode_step(int* out_id, long long* stamps, long long capacity, int* n_barriers, int* n_cta,
+                                 int* khz) {
+  const ModelDims& d = model->dims;
+  B2_CHECK(decode_mode == B200LM_DECODE_PERSISTENT || decode_mode == B200LM_DECODE_PERSISTENT_BASIC,
+           kFailedPrecondition, "the decode timeline needs a persistent decode mode");
+  B2_CUDA(cudaSetDevice(device));
+  const int nb = 5 * d.n_layers + 2;
+  const long long need = (long long)nb * n_sms * 10;     // 2 barrier stamps + 8 in-phase stamps
+  B2_CHECK(stamps != nullptr && capacity >= need, kInvalidArgument,
+           "stamps must hold " + std::to_string(need) + " int64 values");
+  if (!trace_dev) trace_dev = reinterpret_cast<long long*>(alloc(sizeof(long long) * need, true));
+  B2_CUDA(cudaMemsetAsync(trace_dev, 0, sizeof(long long) * need, stream));
+  dargs.trace = trace_dev;
+  dargs.trace_pts = trace_dev + (size_t)nb * n_sms * 2;
+  try {
+    decode_tokens(1, out_id);
+  } catch (...) {
+    dargs.trace = nullptr;
+    dargs.trace_pts = nullptr;
+    throw;
+  }
+  dargs.trace = nullptr;
+  dargs.trace_pts = nullptr;
+  B2_CUDA(cudaMemcpy(stamps, trace_dev, sizeof(long long) * need, cudaMemcpyDeviceToHost));
+  *n_barriers = nb;
+  *n_cta = n_sms;
+  int rate = 0;
+  B2_CUDA(cudaDeviceGetAttribute(&rate, cudaDevAttrClockRate, device));
+  *khz = rate;
 }
 
 void Executor::reset() {
@@ -817,6 +894,14 @@ int B200Lm_ReadKvRow(B200LmExecutor* e, int32_t layer, int32_t is_v, int32_t kv_
   B2_API_BEGIN
   B2_CHECK(e && e->impl && out_row, kInvalidArgument, "null argument");
   e->impl->read_kv_row(layer, is_v, kv_head, pos, out_row, out_page, out_slot);
+  B2_API_END
+}
+
+int B200Lm_TraceDecodeStep(B200LmExecutor* e, int32_t* out_id, int64_t* stamps, int64_t capacity,
+                           int32_t* n_barriers, int32_t* n_cta, int32_t* sm_clock_khz, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out_id && n_barriers && n_cta && sm_clock_khz, kInvalidArgument, "null argument");
+  e->impl->trace_decode_step(out_id, reinterpret_cast<long long*>(stamps), capacity, n_barriers, n_cta, sm_clock_khz);
   B2_API_END
 }
 

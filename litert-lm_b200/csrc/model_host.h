@@ -188,7 +188,7 @@ inline void parallel_for(int64_t n, F fn) {
 
 // mma-tiled layout ("W4T"): 16x64 tiles of 512 bytes ordered [row_tile][k_tile];
 // lane l = 4g + t owns words 0..3; word j covers k = 32*(j/2) + 16*(j%2) + 4t + i,
-// nibble 2i = row g, nibble 2i+1 = row g + 8, stored as q + 8.
+// nibble 2i = row g, nibble 2i+1 = row g + 8, two's complement.
 // row_map(tile_row) gives the source row of each destination row (used to
 // interleave gate and up tiles); rows < 0 are zero rows.
 template <typename RowMap>
@@ -204,8 +204,8 @@ inline void repack_w4t(const uint8_t* packed, int64_t n_dst_rows, int64_t K, Row
           int64_t kq = kt * 64 + 32 * (j >> 1) + 16 * (j & 1) + 4 * t;
           uint32_t w = 0;
           for (int i = 0; i < 4; ++i) {
-            uint32_t a = (uint32_t)((r0 >= 0 ? canon_q(packed, K, r0, kq + i) : 0) + 8);
-            uint32_t b = (uint32_t)((r1 >= 0 ? canon_q(packed, K, r1, kq + i) : 0) + 8);
+            uint32_t a = (uint32_t)(r0 >= 0 ? canon_q(packed, K, r0, kq + i) : 0) & 0xFu;
+            uint32_t b = (uint32_t)(r1 >= 0 ? canon_q(packed, K, r1, kq + i) : 0) & 0xFu;
             w |= a << (8 * i);
             w |= b << (8 * i + 4);
           }

@@ -29,6 +29,7 @@ struct Model {
   const float* embed_scale = nullptr;
   const uint4* head_w = nullptr;
   const float* g_final = nullptr;
+  float gmax_final = 0.f;
   const float* rope_cos[2] = {nullptr, nullptr};
   const float* rope_sin[2] = {nullptr, nullptr};
   std::vector<LayerWeights> layers_host;
@@ -58,6 +59,7 @@ class Executor {
   void decode_tokens(int nsteps, int* out_ids);
   void reset();
   void check_device_error(const char* where);
+  void trace_decode_step(int* out_id, long long* stamps, long long capacity, int* n_barriers, int* n_cta, int* khz);
   void read_kv_row(int layer, int is_v, int kv_head, int pos, float* out, int* page, int* slot);
 
   std::shared_ptr<Model> model;
@@ -91,7 +93,10 @@ class Executor {
   int pages_per_seq = 0;
   DecodeArgs dargs{};
   size_t dec_smem = 0;
+  size_t stream_smem = 0;
+  int stream_half = 0;
   unsigned barrier_epoch = 0;
+  long long* trace_dev = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
   // prefill scratch
   int t_max = 0, t_pad = 0;

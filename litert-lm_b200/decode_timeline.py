@@ -1,0 +1,95 @@
+"""Per-phase device timeline of one decode step (persistent decode modes).
+
+    python litert-lm_b200/decode_timeline.py [--model gemma3-1b] [--mode 2] [--prompt 1024]
+
+Prints, for every phase class (qkv, attention, o-proj, gate/up, down, head, arg-max), the
+time the slowest CTA worked, the barrier latency seen by the last CTA to arrive, and their
+sum over the step.  Built on B200Lm_TraceDecodeStep.
+"""
+from __future__ import annotations
+
+import argparse
+import os
+import sys
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+import __graft_entry__ as graft  # noqa: E402
+
+
+def summarise(stamps: np.ndarray, khz: int, n_layers: int):
+    """stamps [n_barriers, n_cta, 2] -> rows (phase, work_max_us, work_mean_us, barrier_us)."""
+    nb = stamps.shape[0]
+    arrive, release = stamps[:, :, 0].astype(np.float64), stamps[:, :, 1].astype(np.float64)
+    us = 1e3 / khz
+    work = np.zeros_like(arrive)
+    work[1:] = arrive[1:] - release[:-1]
+    work[0] = np.nan                      # phase 0 includes kernel start-up
+    wait = release - arrive
+    names = []
+    for _ in range(n_layers):
+        names += ["qkv", "attention", "o-proj", "gate/up", "down"]
+    names += ["head", "arg-max"]
+    rows = {}
+    for b in range(nb):
+        r = rows.setdefault(names[b], [0.0, 0.0, 0.0, 0])
+        if b > 0:
+            r[0] += np.nanmax(work[b]) * us
+            r[1] += np.nanmean(work[b]) * us
+        r[2] += wait[b].min() * us
+        r[3] += 1
+    return rows
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--model", default="gemma3-1b")
+    ap.add_argument("--mode", type=int, default=2)
+    ap.add_argument("--prompt", type=int, default=1024)
+    args = ap.parse_args()
+    sys.path.insert(0, ROOT)
+    import bench
+    graft.build()
+    pkg = graft.load_package()
+    cfg, rec, img = bench.load_model(args.model)
+    ex = pkg.B200LlmExecutor(img, decode_mode=args.mode)
+    ids = np.random.Generator(np.random.PCG64(cfg.seed)).integers(0, cfg.vocab, args.prompt).astype(np.int32)
+    ex.Prefill(ids)
+    for _ in range(3):
+        ex.Decode()
+    tok, stamps, khz = ex.TraceDecodeStep()
+    rows = summarise(stamps, khz, cfg.n_layers)
+    total = 0.0
+    print(f"model={cfg.name} mode={args.mode} n_cta={stamps.shape[1]} barriers={stamps.shape[0]} sm_clock_khz={khz}")
+    print(f"{'phase':10s} {'count':>5s} {'slowest-CTA work us':>20s} {'mean-CTA work us':>17s} {'barrier us':>11s} {'per-phase us':>13s}")
+    for name, (wmax, wmean, bar, n) in rows.items():
+        total += wmax + bar
+        print(f"{name:10s} {n:5d} {wmax:20.1f} {wmean:17.1f} {bar:11.1f} {(wmax + bar) / n:13.2f}")
+    print(f"step total (work of slowest CTA + barrier latency): {total:.1f} us")
+    pts = getattr(ex, "last_trace_points", None)
+    if pts is not None and pts.any():
+        names = []
+        for _ in range(cfg.n_layers):
+            names += ["qkv", "attention", "o-proj", "gate/up", "down"]
+        names += ["head", "arg-max"]
+        us = 1e3 / khz
+        labels = ["start->staged", "issue next", "prologue", "mma", "epilogue", "tail"]
+        print("segments inside a phase, mean over CTAs that reached both points (us):")
+        for cls in ["qkv", "attention", "o-proj", "gate/up", "down", "head"]:
+            idx = [b for b in range(1, len(names)) if names[b] == cls]
+            seg = []
+            rel = stamps[[b - 1 for b in idx], :, 1].astype(np.float64)
+            p = pts[idx].astype(np.float64)
+            first = np.where(p[:, :, 0] > 0, (p[:, :, 0] - rel) * us, np.nan)
+            seg.append(("release->start", np.nanmean(first)))
+            for k in range(6):
+                ok = (p[:, :, k] > 0) & (p[:, :, k + 1] > 0)
+                d = np.where(ok, (p[:, :, k + 1] - p[:, :, k]) * us, np.nan)
+                seg.append((labels[k], float(np.nanmean(d)) if ok.any() else float("nan")))
+            print(f"  {cls:10s} " + "  ".join(f"{n}={v:.2f}" for n, v in seg))
+
+
+if __name__ == "__main__":
+    main()

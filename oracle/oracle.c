@@ -389,12 +389,14 @@ typedef struct {
   int next_input_token_id; /* -1 = none pending */
   int last_plan_n;
   int last_plan_bucket[64], last_plan_len[64];
+  int n_layers; /* copy: the model may be released first */
 } OrcExec;
 
 OrcExec* orc_exec_create(OrcModel* m) {
   OrcExec* e = (OrcExec*)calloc(1, sizeof *e);
   const OrcCfg* c = &m->cfg;
   e->m = m;
+  e->n_layers = c->n_layers;
   e->n_pages = (c->max_ctx + ORC_PAGE - 1) / ORC_PAGE;
   size_t per = (size_t)e->n_pages * c->hkv * ORC_PAGE * c->hd;
   e->kcache = (float**)calloc((size_t)c->n_layers, sizeof(float*));
@@ -410,7 +412,7 @@ OrcExec* orc_exec_create(OrcModel* m) {
 
 void orc_exec_destroy(OrcExec* e) {
   if (!e) return;
-  for (int i = 0; i < e->m->cfg.n_layers; ++i) { free(e->kcache[i]); free(e->vcache[i]); }
+  for (int i = 0; i < e->n_layers; ++i) { free(e->kcache[i]); free(e->vcache[i]); }
   free(e->kcache); free(e->vcache); free(e);
 }
 

@@ -29,8 +29,8 @@ def run_pair(pkg, orc, models, name, prompt, steps, **kw):
 
 
 @pytest.mark.parametrize("name,prompt_len,mode,gemm", [
-    ("tiny", 32, 1, 1), ("tiny", 32, 2, 1), ("tiny", 32, 2, 2), ("small", 200, 1, 1), ("small", 200, 2, 2),
-    ("small", 300, 2, 2), ("small-gqa", 150, 2, 2), ("small-gqa", 150, 1, 1),
+    ("tiny", 32, 1, 1), ("tiny", 32, 2, 1), ("tiny", 32, 2, 2), ("tiny", 32, 3, 2), ("small", 200, 1, 1),
+    ("small", 200, 2, 2), ("small", 300, 2, 2), ("small", 300, 3, 1), ("small-gqa", 150, 2, 2), ("small-gqa", 150, 1, 1),
 ])
 def test_logits_and_greedy_tokens_match_oracle(pkg, orc, models, name, prompt_len, mode, gemm):
     """Teacher-forced on the oracle's token every step, so one flip cannot hide later errors."""

@@ -40,7 +40,7 @@ def test_header_compiles_as_c():
 
 def w4t_elements(buf, n, k):
     """Expands the decode layout exactly as documented: 16x64 tiles of 512 bytes, lane 4g+t,
-    word j covers k = 32*(j/2) + 16*(j%2) + 4t + i, nibble 2i = row g, 2i+1 = row g+8, q+8."""
+    word j covers k = 32*(j/2) + 16*(j%2) + 4t + i, nibble 2i = row g, 2i+1 = row g+8, two's complement."""
     words = buf.view(np.uint32).reshape(n // 16, k // 64, 32, 4)
     out = np.zeros((n, k), dtype=np.int8)
     for lane in range(32):
@@ -49,8 +49,10 @@ def w4t_elements(buf, n, k):
             w = words[:, :, lane, j]
             for i in range(4):
                 kk = 32 * (j // 2) + 16 * (j % 2) + 4 * t + i
-                lo = ((w >> (8 * i)) & 0xF).astype(np.int16) - 8
-                hi = ((w >> (8 * i + 4)) & 0xF).astype(np.int16) - 8
+                lo = ((w >> (8 * i)) & 0xF).astype(np.int16)
+                hi = ((w >> (8 * i + 4)) & 0xF).astype(np.int16)
+                lo = np.where(lo >= 8, lo - 16, lo)
+                hi = np.where(hi >= 8, hi - 16, hi)
                 out[g::16, kk::64] = lo
                 out[g + 8::16, kk::64] = hi
     return out
