@@ -16,8 +16,12 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "libb200lm.so")
 SOURCES = ["lib.cu"]
-DEPS = ["lib.cu", "executor.cu", "ops.cu", "common.cuh", "decode_ops.cuh", "prefill_ops.cuh", "model_host.h",
-        "runtime.h", os.path.join("..", "..", "include", "b200lm.h"), os.path.join("..", "..", "include", "b200lm_ops.h")]
+def _deps():
+    """Every file the translation unit can include."""
+    inc = os.path.join(HERE, "..", "include")
+    files = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cu", ".cuh", ".h"))]
+    files += [os.path.join(inc, f) for f in os.listdir(inc) if f.endswith(".h")]
+    return files
 
 
 def nvcc_path() -> str:
@@ -31,7 +35,7 @@ def needs_build() -> bool:
     if not os.path.exists(LIB):
         return True
     t = os.path.getmtime(LIB)
-    return any(os.path.getmtime(os.path.join(CSRC, d)) > t for d in DEPS)
+    return any(os.path.getmtime(d) > t for d in _deps())
 
 
 def build(force: bool = False, verbose: bool = False) -> str:

@@ -86,9 +86,9 @@ __host__ __device__ inline size_t stream_fixed_bytes(const ModelDims& d, int nco
   int kmax = stream_kmax(d);
   size_t act = (size_t)ncols * kmax * 4;                          // xf
   act += (size_t)ncols * 3 * dec_xstride(kmax);                   // xq (three terms)
-  act += (size_t)kMaxRoundUnits * 16 * kQCols * 4;                // red
   size_t attn = stream_attn_bytes(d);
-  if (attn > act) act = attn;                                     // attention aliases the GEMV staging
+  if (attn > act) act = attn;                                     // attention aliases xf / xq only
+  act += (size_t)kMaxRoundUnits * 16 * kQCols * 4 + 16;           // red (kept zero between rounds: never aliased)
   size_t b = act + 64 * 4 + kMaxCols * 4 + 2 * kDecThreads * 4;   // scratch, colscale, argbuf
   b += (size_t)d.n_layers * (sizeof(LayerWeights) + sizeof(LayerKv)) + 6 * sizeof(PhasePlan);
   b += 128 + 2 * sizeof(FillDesc) + 64;                           // mbarriers, descriptors, flags
@@ -112,11 +112,11 @@ __device__ __forceinline__ void stream_carve(unsigned char* base, const ModelDim
   c.s.xf = reinterpret_cast<float*>(p); p += (size_t)ncols * kmax * 4;
   c.s.xstride = dec_xstride(kmax);
   c.s.xq = reinterpret_cast<int8_t*>(p); p += (size_t)ncols * 3 * c.s.xstride;
-  c.s.red = reinterpret_cast<int*>(p); p += (size_t)kMaxRoundUnits * 16 * kQCols * 4;
   size_t attn = stream_attn_bytes(d);
   if ((size_t)(p - act0) < attn) p = act0 + attn;
   p = reinterpret_cast<unsigned char*>(((uintptr_t)p + 15) & ~(uintptr_t)15);
   c.s.attn = reinterpret_cast<float*>(act0);
+  c.s.red = reinterpret_cast<int*>(p); p += (size_t)kMaxRoundUnits * 16 * kQCols * 4;
   c.s.scratch = reinterpret_cast<float*>(p); p += 64 * 4;
   c.s.colscale = reinterpret_cast<float*>(p); p += kMaxCols * 4;
   c.s.colsum = nullptr;

@@ -375,7 +375,7 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   if (e->decode_mode == B200LM_DECODE_PERSISTENT) {
     // staging halves take what shared memory the activation staging leaves, up to 96 KiB each
     size_t fixed = stream_fixed_bytes(d, a.ncols);
-    long room = ((long)prop.sharedMemPerBlockOptin - (long)fixed) / 2;
+    long room = ((long)prop.sharedMemPerBlockOptin - (long)fixed - 2048) / 2;   // margin: static shared memory
     int half = (int)std::min<long>(room, 96 * 1024) / 1024 * 1024;
     bool ok = half > 0 && stream_model_fits(d, a.o_slices, a.down_slices, half) && prop.cooperativeLaunch;
     if (ok) {
