@@ -75,7 +75,8 @@ def main() -> None:
             names += ["qkv", "attention", "o-proj", "gate/up", "down"]
         names += ["head", "arg-max"]
         us = 1e3 / khz
-        labels = ["start->staged", "issue next", "prologue", "mma", "epilogue", "tail"]
+        points = [0, 1, 3, 4, 5, 6]           # stamps taken by the streaming kernel (2 is unused)
+        labels = ["wait staged", "prologue", "mma", "epilogue", "tail rounds"]
         print("segments inside a phase, mean over CTAs that reached both points (us):")
         for cls in ["qkv", "attention", "o-proj", "gate/up", "down", "head"]:
             idx = [b for b in range(1, len(names)) if names[b] == cls]
@@ -84,10 +85,14 @@ def main() -> None:
             p = pts[idx].astype(np.float64)
             first = np.where(p[:, :, 0] > 0, (p[:, :, 0] - rel) * us, np.nan)
             seg.append(("release->start", np.nanmean(first)))
-            for k in range(6):
-                ok = (p[:, :, k] > 0) & (p[:, :, k + 1] > 0)
-                d = np.where(ok, (p[:, :, k + 1] - p[:, :, k]) * us, np.nan)
+            for k in range(len(points) - 1):
+                lo, hi = points[k], points[k + 1]
+                ok = (p[:, :, lo] > 0) & (p[:, :, hi] > 0)
+                d = np.where(ok, (p[:, :, hi] - p[:, :, lo]) * us, np.nan)
                 seg.append((labels[k], float(np.nanmean(d)) if ok.any() else float("nan")))
+            arr = stamps[idx, :, 0].astype(np.float64)
+            lastp = np.where(p[:, :, 6] > 0, (arr - p[:, :, 6]) * us, np.nan)
+            seg.append(("end->arrive", float(np.nanmean(lastp)) if np.isfinite(lastp).any() else float("nan")))
             print(f"  {cls:10s} " + "  ".join(f"{n}={v:.2f}" for n, v in seg))
 
 
