@@ -60,6 +60,39 @@ int B200LmOps_Attention(int32_t device, const float* q, const float* k, const fl
                         int32_t kv_bf16, int32_t nsplit, int32_t repeat, float* out, float* ms_out,
                         char** err);
 
+/* Split-KV decode attention that allocates nothing.  It has no counterpart in
+ * the reference.  It is for callers that may not allocate device memory when
+ * they call in: code running inside another runtime's execution callback, a
+ * serving loop that bans allocator calls once it is warm, or a process whose
+ * GPU memory was handed out completely at start-up.  The ordinary entry point
+ * above allocates scratch for the per-split partial results on every call;
+ * this one keeps them (with the query positions and an error word) in one
+ * fixed 8 MiB device array that is part of the library image, so every GPU
+ * that loads the library holds those 8 MiB until the process ends.
+ *
+ * All pointers are DEVICE memory owned by the caller:
+ *   q_dev          [batch] rows of (hq + 2*hkv)*hd floats, the layout of a fused
+ *                  QKV projection; only the first hq*hd floats of a row are read
+ *   k_pages_dev,   paged cache [page][hkv][256][hd], fp32 or bf16 (kv_bf16),
+ *   v_pages_dev    already holding positions 0 .. s-1
+ *   page_table_dev [ceil(s/256)] physical page of each logical page
+ *   out_dev        [batch][hq][hd] floats
+ * Every query sits at position s-1 (causal; window <= 0 means global).  Work is
+ * queued on `stream` (NULL: the default stream) and the call returns without
+ * waiting.
+ *
+ * Limits: batch <= 16368 and batch*hq*nsplit*(hd+2)*4 bytes <= 8 MiB - 64 KiB;
+ * larger requests are rejected with InvalidArgument.  The first call on a
+ * device looks up the array's address and sets a kernel attribute; make that
+ * first call before starting any stream capture.  All calls on a device share
+ * the array, which keeps what the last call left in it (the call itself resets
+ * the one word that must start at zero); two calls whose kernels overlap on
+ * the GPU -- different streams, no ordering between them -- race on it. */
+int B200LmOps_AttentionDecodeStatic(int32_t device, const float* q_dev, const void* k_pages_dev,
+                                    const void* v_pages_dev, const int32_t* page_table_dev, int32_t batch, int32_t s,
+                                    int32_t hq, int32_t hkv, int32_t hd, int32_t window, int32_t kv_bf16,
+                                    int32_t nsplit, float* out_dev, void* stream, char** err);
+
 #ifdef __cplusplus
 }
 #endif

@@ -56,7 +56,7 @@ _EXEC_SYMBOLS = ["B200Lm_Create", "B200Lm_CreateShared", "B200Lm_Destroy", "B200
                  "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_BackendName", "B200Lm_Synchronize",
                  "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount", "B200Lm_TraceDecodeStep"]
 _OPS_SYMBOLS = ["B200LmOps_RepackW4T", "B200LmOps_RepackW4G", "B200LmOps_UnpackW4", "B200LmOps_GemvW4",
-                "B200LmOps_GemmW4", "B200LmOps_GemmGegluW4", "B200LmOps_Attention"]
+                "B200LmOps_GemmW4", "B200LmOps_GemmGegluW4", "B200LmOps_Attention", "B200LmOps_AttentionDecodeStatic"]
 
 
 def load_library() -> C.CDLL:
@@ -93,6 +93,7 @@ def load_library() -> C.CDLL:
         "B200LmOps_GemmW4": [i32, i32, vp, vp, i64, i64, vp, i32, i32, i32, vp, vp, errp],
         "B200LmOps_GemmGegluW4": [i32, i32, vp, vp, vp, vp, i64, i64, vp, i32, vp, errp],
         "B200LmOps_Attention": [i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, errp],
+        "B200LmOps_AttentionDecodeStatic": [i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, errp],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)
@@ -330,3 +331,14 @@ class ops:
         _call("B200LmOps_Attention", device, _ptr(q), _ptr(k), _ptr(v), t, s, hq, hkv, hd, qpos0, window, int(kv_bf16),
               nsplit, repeat, _ptr(out), C.byref(ms))
         return out, ms.value
+
+    @staticmethod
+    def attention_decode_static(q_dev: int, k_pages_dev: int, v_pages_dev: int, page_table_dev: int, out_dev: int,
+                                batch: int, s: int, hq: int, hkv: int, hd: int, window: int = 0, kv_bf16: bool = False,
+                                nsplit: int = 8, stream: int = 0, device: int = 0) -> None:
+        """Split-KV decode attention over caller-owned DEVICE buffers (raw addresses); allocates
+        nothing: the split partials live in a fixed array inside the library (8 MiB per GPU).
+        For callers that must not allocate device memory at call time."""
+        _call("B200LmOps_AttentionDecodeStatic", device, C.c_void_p(q_dev), C.c_void_p(k_pages_dev),
+              C.c_void_p(v_pages_dev), C.c_void_p(page_table_dev), batch, s, hq, hkv, hd, window, int(kv_bf16), nsplit,
+              C.c_void_p(out_dev), C.c_void_p(stream) if stream else None)

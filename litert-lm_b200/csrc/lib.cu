@@ -2,3 +2,4 @@
 // executor and the operator-level ABI are compiled together.
 #include "executor.cu"
 #include "ops.cu"
+#include "ops_static.cu"
