@@ -44,8 +44,9 @@ struct LayerWeights {
 struct LayerKv {
   void* k;               // [pages][hkv][kPage][hd], fp32 or bf16
   void* v;
-  __nv_bfloat16* k16;    // bf16 shadow of an fp32 cache (tensor-core prefill), or null
-  __nv_bfloat16* v16;
+  // operands of the tensor-core prefill attention, or null when it is not used:
+  __nv_bfloat16* k16;    // bf16 copy of K rows, same layout (null when the cache itself is bf16)
+  __nv_bfloat16* v16;    // bf16 V TRANSPOSED per page: [page][kv_head][hd][kPage]
 };
 
 struct DecodeState {          // lives in device memory, one per executor
@@ -97,14 +98,16 @@ __device__ __forceinline__ void dec_sync() { asm volatile("bar.sync 1, 512;" :::
 
 // ----------------------------------------------------------------- reductions
 
+// The per-warp partials meet in shared memory; every warp then folds the 16 of
+// them with shuffles (one load per lane instead of 16 per thread).
 __device__ __forceinline__ float block_sum(float v, float* scratch) {
   v = warp_sum(v);
   dec_sync();
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
   dec_sync();
-  float t = 0.f;
+  float t = scratch[threadIdx.x & (kDecWarps - 1)];
 #pragma unroll
-  for (int i = 0; i < kDecWarps; ++i) t += scratch[i];
+  for (int o = kDecWarps / 2; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
   return t;
 }
 __device__ __forceinline__ float block_max(float v, float* scratch) {
@@ -112,9 +115,9 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
   dec_sync();
   if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = v;
   dec_sync();
-  float t = scratch[0];
+  float t = scratch[threadIdx.x & (kDecWarps - 1)];
 #pragma unroll
-  for (int i = 1; i < kDecWarps; ++i) t = fmaxf(t, scratch[i]);
+  for (int o = kDecWarps / 2; o > 0; o >>= 1) t = fmaxf(t, __shfl_xor_sync(0xffffffffu, t, o));
   return t;
 }
 
@@ -291,7 +294,7 @@ __device__ __forceinline__ void quantize_value(float r, int nterms, int8_t* q0, 
 }
 
 // Quantises xf[ncols][K] (shared) into xq with nterms int8 terms per column.
-__device__ inline void quantize_cols(const DecodeSmem& s, int K, int ncols, int nterms) {
+__device__ __noinline__ void quantize_cols(const DecodeSmem& s, int K, int ncols, int nterms) {
   for (int col = 0; col < ncols; ++col) {
     const float* x = s.xf + (size_t)col * K;
     float m = 0.f;
@@ -621,14 +624,12 @@ __device__ inline void attn_item(const ModelDims& dm, const AttnJob& j, float* s
       if constexpr (sizeof(T) == 4) {
         kbase[off + e] = k_s[e];
         vbase[off + e] = v_s[e];
-        if (j.kv.k16) {
-          j.kv.k16[off + e] = __float2bfloat16(k_s[e]);
-          j.kv.v16[off + e] = __float2bfloat16(v_s[e]);
-        }
+        if (j.kv.k16) j.kv.k16[off + e] = __float2bfloat16(k_s[e]);
       } else {
         kbase[off + e] = __float2bfloat16(k_s[e]);
         vbase[off + e] = __float2bfloat16(v_s[e]);
       }
+      if (j.kv.v16) j.kv.v16[(((size_t)page * dm.hkv + kvh) * HD + e) * kPage + slot] = __float2bfloat16(v_s[e]);
     }
     // later steps fetch these rows with bulk async copies
     asm volatile("fence.proxy.async.global;" ::: "memory");
@@ -940,7 +941,7 @@ __device__ inline void phase_head(const DecodeArgs& a, const DecodeSmem& s, int 
 }
 
 // Final arg-max over the per-CTA candidates; optionally feeds the token back.
-__device__ inline void phase_argmax(const DecodeArgs& a, int ncta_head) {
+__device__ __noinline__ void phase_argmax(const DecodeArgs& a, int ncta_head) {
   if (threadIdx.x < 32) {
     for (int col = 0; col < a.ncols; ++col) {
       float bv = -INFINITY;

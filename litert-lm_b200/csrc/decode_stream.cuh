@@ -162,7 +162,7 @@ __host__ inline bool stream_model_fits(const ModelDims& d, int o_slices, int dow
   return half_bytes >= 2 * d.hd * esz + d.hd * 4 + 64;   // at least one staged K/V row pair + RoPE row
 }
 
-__device__ __forceinline__ void stream_make_plans(const DecodeArgs& a, StreamCtx& c, int cta, int ncta) {
+__device__ __noinline__ void stream_make_plans(const DecodeArgs& a, StreamCtx& c, int cta, int ncta) {
   const int phases[5] = {kSA, kSC, kSD, kSE, kSH};
   for (int i = 0; i < 5; ++i) {
     PhasePlan& p = c.plan[phases[i]];
@@ -189,7 +189,7 @@ __device__ __forceinline__ void stream_advance(StreamCursor& cur, const StreamCt
 
 // ------------------------------------------------------------ producer warp
 
-__device__ __forceinline__ void stream_producer(const DecodeArgs& a, StreamCtx& c, int cta, int nsteps) {
+__device__ __noinline__ void stream_producer(const DecodeArgs& a, StreamCtx& c, int cta, int nsteps) {
   const int lane = threadIdx.x & 31;
   const ModelDims& dm = a.dims;
   const int last = dm.n_layers - 1;
@@ -338,9 +338,10 @@ __device__ __forceinline__ void gemv_tiles_smem(const uint4* wsm, int ktn, int n
   const int8_t* xrow = xc.q + (size_t)g * xc.stride + 4 * t;
   int acc[4] = {0, 0, 0, 0};
   int cur = -1;
+  int un = beg / ktn, kt = beg - un * ktn - 1;
 #pragma unroll 2
   for (int b = beg; b < end; ++b) {
-    int un = b / ktn, kt = b - un * ktn;
+    if (++kt == ktn) { kt = 0; ++un; }
     uint4 w = wsm[(size_t)b * 32 + lane];
     if (un != cur) {
       if (cur >= 0) flush_tile(red, cur, acc, lane, xc.nq);
@@ -372,9 +373,9 @@ __device__ __forceinline__ void block_sum4(float (&v)[4], float* scratch) {
   dec_sync();
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    float s = 0.f;
+    float s = scratch[k * kDecWarps + (threadIdx.x & (kDecWarps - 1))];
 #pragma unroll
-    for (int i = 0; i < kDecWarps; ++i) s += scratch[k * kDecWarps + i];
+    for (int o = kDecWarps / 2; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
     v[k] = s;
   }
 }
@@ -403,7 +404,7 @@ __device__ __forceinline__ void quantize4(float4 r, int nterms, int8_t* q0, int 
 // One pass over L2 (16-byte loads held in registers), one block reduction.
 __device__ __forceinline__ void stream_prologue_resid(const DecodeArgs& a, StreamCtx& c, int cta, const float* parts,
                                                       int nparts, const float* xin, float* xout, const float* g_post,
-                                                      const float* g_pre, float gmax_pre) {
+                                                      const float* g_pre, float gmax_pre, int bar) {
   const int d = a.dims.d, d4 = d / 4;
   const DecodeSmem& s = c.s;
   const float bound = sqrtf((float)d) * gmax_pre * 1.0001f;     // |rmsnorm(x)_i g_i| never exceeds it
@@ -435,7 +436,9 @@ __device__ __forceinline__ void stream_prologue_resid(const DecodeArgs& a, Strea
       sums[3] += fg.x * fg.x + fg.y * fg.y + fg.z * fg.z + fg.w * fg.w;
       gp[u] = fg;
     }
+    if (col == 0) B2_TP(2);
     block_sum4(sums, s.scratch);
+    if (col == 0) B2_TP(7);
     const float r = rsqrtf(sums[0] / (float)d + a.dims.eps);
     const float ss2 = fmaxf(sums[1] + 2.0f * r * sums[2] + r * r * sums[3], 0.f);
     const float r2 = rsqrtf(ss2 / (float)d + a.dims.eps);
@@ -456,7 +459,7 @@ __device__ __forceinline__ void stream_prologue_resid(const DecodeArgs& a, Strea
   dec_sync();
 }
 
-__device__ __forceinline__ void stream_prologue_embed(const DecodeArgs& a, StreamCtx& c, int cta, float* xout,
+__device__ __noinline__ void stream_prologue_embed(const DecodeArgs& a, StreamCtx& c, int cta, float* xout,
                                                       const float* g_pre, float gmax_pre) {
   const int d = a.dims.d;
   const DecodeSmem& s = c.s;
@@ -583,16 +586,18 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
   if (it.split == 0) {     // KV append: exactly one CTA per (query, kv head)
     T* kbase = reinterpret_cast<T*>(kv.k);
     T* vbase = reinterpret_cast<T*>(kv.v);
-    size_t off = (((size_t)ptab[pos / kPage] * dm.hkv + kvh) * kPage + (pos % kPage)) * HD;
+    const int page = ptab[pos / kPage], slot = pos % kPage;
+    size_t off = (((size_t)page * dm.hkv + kvh) * kPage + slot) * HD;
     for (int e = threadIdx.x; e < HD; e += kDecThreads) {
       if constexpr (sizeof(T) == 4) {
         kbase[off + e] = k_s[e];
         vbase[off + e] = v_s[e];
-        if (kv.k16) { kv.k16[off + e] = __float2bfloat16(k_s[e]); kv.v16[off + e] = __float2bfloat16(v_s[e]); }
+        if (kv.k16) kv.k16[off + e] = __float2bfloat16(k_s[e]);
       } else {
         kbase[off + e] = __float2bfloat16(k_s[e]);
         vbase[off + e] = __float2bfloat16(v_s[e]);
       }
+      if (kv.v16) kv.v16[(((size_t)page * dm.hkv + kvh) * HD + e) * kPage + slot] = __float2bfloat16(v_s[e]);
     }
   }
   int k0, k1;
@@ -715,32 +720,6 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
   dec_sync();
 }
 
-template <typename T, int HD>
-__device__ __forceinline__ void attn_smem_g(const DecodeArgs& a, StreamCtx& c, const AttnItem& it, unsigned char* hb) {
-  switch (a.dims.hq / a.dims.hkv) {
-    case 1: attn_smem_item<T, HD, 1>(a, c, it, hb); break;
-    case 2: attn_smem_item<T, HD, 2>(a, c, it, hb); break;
-    default: attn_smem_item<T, HD, 4>(a, c, it, hb); break;
-  }
-}
-__device__ __forceinline__ void attn_smem_dispatch(const DecodeArgs& a, StreamCtx& c, const AttnItem& it, unsigned char* hb) {
-  if (a.dims.kv_dtype == 0) {
-    switch (a.dims.hd) {
-      case 32: attn_smem_g<float, 32>(a, c, it, hb); break;
-      case 64: attn_smem_g<float, 64>(a, c, it, hb); break;
-      case 128: attn_smem_g<float, 128>(a, c, it, hb); break;
-      default: attn_smem_g<float, 256>(a, c, it, hb); break;
-    }
-  } else {
-    switch (a.dims.hd) {
-      case 32: attn_smem_g<__nv_bfloat16, 32>(a, c, it, hb); break;
-      case 64: attn_smem_g<__nv_bfloat16, 64>(a, c, it, hb); break;
-      case 128: attn_smem_g<__nv_bfloat16, 128>(a, c, it, hb); break;
-      default: attn_smem_g<__nv_bfloat16, 256>(a, c, it, hb); break;
-    }
-  }
-}
-
 // Log-sum-exp combine of the split partials of one head slice into xf (then quantised).
 // All loads of a thread are independent, so they overlap.
 __device__ __forceinline__ void stream_prologue_combine(const DecodeArgs& a, StreamCtx& c, int layer) {
@@ -796,12 +775,14 @@ __device__ __forceinline__ void stream_prologue_combine(const DecodeArgs& a, Str
 }
 
 // One GEMV phase of the stream: for every round acquire / (prologue) / MMA / epilogue / release.
-template <typename Prologue>
-__device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx& c, int ph, float* y, Prologue prologue,
+// Called from ONE place (the phase loop of the kernel), so its code exists once.
+__device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx& c, int ph, int layer, int cta,
                                                   float* best_val, int* best_idx, int bar) {
   const PhasePlan& p = c.plan[ph];
+  const ModelDims& dm = a.dims;
   const int ncols = a.ncols, nterms = a.nterms;
   const int fills = p.rounds > 1 ? p.rounds : 1;
+  float* y = ph == kSA ? a.qkv : ph == kSC ? a.opart : ph == kSD ? a.act : ph == kSE ? a.fpart : a.logits;
   for (int r = 0; r < fills; ++r) {
     unsigned char* hb;
     if (r == 0) B2_TP(0);
@@ -812,18 +793,43 @@ __device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx
       const int ntile = fd->ntile, ktn = fd->ktn, ta = fd->ta;
       const uint4* wsm = reinterpret_cast<const uint4*>(hb);
       const float* ssm = reinterpret_cast<const float*>(hb + (size_t)ntile * ktn * 512);
-      const float* gsm = ssm + ntile * 16;          // g_pre then g_post (round 0 of norm phases)
-      if (r == 0) prologue(gsm, gsm + a.dims.d);
-      if (r == 0) B2_TP(3);
+      const float* g_pre = ssm + ntile * 16;          // round 0 of norm phases: g_pre then g_post
+      const float* g_post = g_pre + dm.d;
+      if (r == 0) {
+        const LayerWeights& L = c.lw[layer];
+        if (ph == kSA && layer == 0) {
+          stream_prologue_embed(a, c, cta, a.xres[1], g_pre, L.gmax_pre_attn);
+        } else if (ph == kSC) {
+          stream_prologue_combine(a, c, layer);
+        } else if (ph == kSE) {
+          const int Ks = dm.ffn / a.down_slices;
+          for (int col = 0; col < a.ncols; ++col)
+            for (int i = threadIdx.x; i < Ks / 4; i += kDecThreads)
+              reinterpret_cast<float4*>(c.s.xf + (size_t)col * Ks)[i] =
+                  __ldcg(reinterpret_cast<const float4*>(a.act + (size_t)col * dm.ffn + (size_t)p.slice * Ks) + i);
+          dec_sync();
+          quantize_cols(c.s, Ks, a.ncols, a.nterms);
+        } else {
+          // A (layer > 0), D and H: residual update + two norms, one reduction
+          const bool isD = ph == kSD;
+          const float* parts = isD ? a.opart : a.fpart;
+          const int nparts = isD ? a.o_slices : a.down_slices;
+          const float* xin = isD ? a.xres[1] : a.xres[0];
+          float* xout = isD ? a.xres[0] : a.xres[1];
+          const float gmax = ph == kSH ? a.gmax_final : isD ? L.gmax_pre_ffn : L.gmax_pre_attn;
+          stream_prologue_resid(a, c, cta, parts, nparts, xin, xout, g_post, g_pre, gmax, bar);
+        }
+        B2_TP(3);
+      }
       QuantCols xc{c.s.xq, c.s.xstride, ncols * nterms};
       gemv_tiles_smem(wsm, ktn, ntile, xc, c.s.red);
       dec_sync();
       if (r == 0) B2_TP(4);
       if (p.epilogue == kEpiGeglu) {
         const int npair = ntile / 2;
-        for (int i = threadIdx.x; i < npair * 16 * ncols; i += kDecThreads) {
-          int col = i / (npair * 16), rem = i - col * npair * 16;
-          int pr = rem / 16, row = rem & 15;
+        for (int col = 0; col < ncols; ++col)
+        for (int i = threadIdx.x; i < npair * 16; i += kDecThreads) {
+          int pr = i >> 4, row = i & 15;
           float gate = finalize_value(c.s, 2 * pr, row, col, nterms) * ssm[(2 * pr) * 16 + row];
           float up = finalize_value(c.s, 2 * pr + 1, row, col, nterms) * ssm[(2 * pr + 1) * 16 + row];
           y[(size_t)col * (p.N / 2) + (size_t)(ta / 2 + pr) * 16 + row] = gelu_tanh(gate) * up;
@@ -833,9 +839,9 @@ __device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx
           }
         }
       } else {
-        for (int i = threadIdx.x; i < ntile * 16 * ncols; i += kDecThreads) {
-          int col = i / (ntile * 16), rem = i - col * ntile * 16;
-          int un = rem / 16, row = rem & 15;
+        for (int col = 0; col < ncols; ++col)
+        for (int i = threadIdx.x; i < ntile * 16; i += kDecThreads) {
+          int un = i >> 4, row = i & 15;
           int n = (ta + un) * 16 + row;
           float v = finalize_value(c.s, un, row, col, nterms) * ssm[un * 16 + row];
           y[((size_t)p.slice * ncols + col) * p.N + n] = v;
@@ -852,6 +858,11 @@ __device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx
   B2_TP(6);
 }
 
+// The kernel is instantiated per cache type / head_dim / GQA group, so the loop
+// over phases carries exactly one attention variant and one GEMV phase body:
+// every phase's code runs once per layer, and a small loop body stays in the
+// instruction cache.
+template <typename T, int HD, int G>
 __global__ void __launch_bounds__(kStreamThreads, 1)
 decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned int epoch0, int half_bytes) {
   extern __shared__ __align__(128) unsigned char ssm_raw[];
@@ -872,8 +883,8 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
     c.lkv[i] = a.kv[i];
   }
   for (int i = threadIdx.x; i < kMaxRoundUnits * 16 * kQCols; i += kStreamThreads) c.s.red[i] = 0;
-  const int esz_kv = dm.kv_dtype == 0 ? 4 : 2;
-  c.npre_max = min(kStreamMaxStagedRows, (half_bytes - dm.hd * 4) / (2 * dm.hd * esz_kv));
+  constexpr int esz_kv = (int)sizeof(T);
+  c.npre_max = min(kStreamMaxStagedRows, (half_bytes - HD * 4) / (2 * HD * esz_kv));
   c.wait_no = 0;
   c.aux_cnt = 0;
   __syncthreads();
@@ -881,31 +892,27 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
   __syncthreads();
 
   if (threadIdx.x >= kDecThreads) {       // ---- producer warp
+#ifndef B2_SZ_NO_PRODUCER
     stream_producer(a, c, cta, nsteps);
+#endif
     return;
   }
 
   int bar = 0;
+  const int n_phases = 5 * dm.n_layers + 1;
   for (int step = 0; step < nsteps; ++step) {
     if (threadIdx.x == 0) *c.step_ready = step + 1;
-    for (int layer = 0; layer < dm.n_layers; ++layer) {
-      const LayerWeights& L = c.lw[layer];
-      // ---- A: residual + pre-attention norm -> QKV
-      if (layer == 0) {
-        stream_gemv_phase(a, c, kSA, a.qkv,
-                          [&](const float* g_pre, const float*) { stream_prologue_embed(a, c, cta, a.xres[1], g_pre, L.gmax_pre_attn); },
-                          nullptr, nullptr, bar);
-      } else {
-        stream_gemv_phase(a, c, kSA, a.qkv,
-                          [&](const float* g_pre, const float* g_post) {
-                            stream_prologue_resid(a, c, cta, a.fpart, a.down_slices, a.xres[0], a.xres[1], g_post, g_pre,
-                                                  L.gmax_pre_attn);
-                          },
-                          nullptr, nullptr, bar);
-      }
-      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
-      // ---- B: attention (K/V rows and the RoPE row staged by the producer)
-      {
+    float bv[kMaxCols];
+    int bi[kMaxCols];
+#pragma unroll
+    for (int cc = 0; cc < kMaxCols; ++cc) { bv[cc] = -INFINITY; bi[cc] = 0x7fffffff; }
+#pragma unroll 1
+    for (int pi = 0; pi < n_phases; ++pi) {
+      int layer = pi / 5, ph = pi - layer * 5;       // A, B, C, D, E of each layer ...
+      if (pi == n_phases - 1) { layer = dm.n_layers - 1; ph = kSH; }   // ... then the head
+      if (ph == kSB) {
+        // ---- attention (K/V rows and the RoPE row staged by the producer)
+        const LayerWeights& L = c.lw[layer];
         unsigned char* hb;
         B2_TP(0);
         const FillDesc* fd = stream_acquire(c, &hb, &a.st->err);
@@ -914,7 +921,7 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
         const int is_global = L.is_global;
         const int nsplit = is_global ? a.n_attn_splits_global : a.n_attn_splits_local;
         const int items = a.ncols * dm.hkv * nsplit;
-        const size_t rowb = (size_t)dm.hd * esz_kv;
+        const size_t rowb = (size_t)HD * esz_kv;
         for (int itx = cta; itx < items; itx += ncta) {
           AttnItem it;
           it.layer = layer;
@@ -927,87 +934,68 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
           if (itx == cta && fd->valid && fd->ph == kSB) {
             it.nstaged = fd->npre;
             it.cos_r = reinterpret_cast<const float*>(hb + (size_t)2 * c.npre_max * rowb);
-            it.sin_r = it.cos_r + dm.hd / 2;
+            it.sin_r = it.cos_r + HD / 2;
           } else {            // further items of this CTA: rows fetched on the spot
             int pos = __ldcg(&a.st->pos[it.col]);
             if (pos < 0 || pos >= dm.max_ctx) pos = 0;
             it.nstaged = -1;
-            it.cos_r = a.rope_cos[is_global ? 1 : 0] + (size_t)pos * (dm.hd / 2);
-            it.sin_r = a.rope_sin[is_global ? 1 : 0] + (size_t)pos * (dm.hd / 2);
+            it.cos_r = a.rope_cos[is_global ? 1 : 0] + (size_t)pos * (HD / 2);
+            it.sin_r = a.rope_sin[is_global ? 1 : 0] + (size_t)pos * (HD / 2);
           }
-          attn_smem_dispatch(a, c, it, hb);
+#ifndef B2_SZ_NO_ATTN
+          attn_smem_item<T, HD, G>(a, c, it, hb);
+#endif
         }
         B2_TP(4);
         stream_release(c);
+      } else {
+#ifndef B2_SZ_NO_GEMV
+        stream_gemv_phase(a, c, ph, layer, cta, bv, bi, bar);
+#endif
       }
-      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
-      // ---- C: combine partials of one head slice -> O projection
-      stream_gemv_phase(a, c, kSC, a.opart, [&](const float*, const float*) { stream_prologue_combine(a, c, layer); },
-                        nullptr, nullptr, bar);
-      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
-      // ---- D: post-attention norm + residual + pre-FFN norm -> gate/up + GeGLU
-      stream_gemv_phase(a, c, kSD, a.act,
-                        [&](const float* g_pre, const float* g_post) {
-                          stream_prologue_resid(a, c, cta, a.opart, a.o_slices, a.xres[1], a.xres[0], g_post, g_pre,
-                                                L.gmax_pre_ffn);
-                        },
-                        nullptr, nullptr, bar);
-      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
-      // ---- E: activation slice -> down projection
-      stream_gemv_phase(a, c, kSE, a.fpart,
-                        [&](const float*, const float*) {
-                          const PhasePlan& p = c.plan[kSE];
-                          const int Ks = dm.ffn / a.down_slices;
-                          for (int col = 0; col < a.ncols; ++col)
-                            for (int i = threadIdx.x; i < Ks / 4; i += kDecThreads)
-                              reinterpret_cast<float4*>(c.s.xf + (size_t)col * Ks)[i] =
-                                  __ldcg(reinterpret_cast<const float4*>(a.act + (size_t)col * dm.ffn + (size_t)p.slice * Ks) + i);
-                          dec_sync();
-                          quantize_cols(c.s, Ks, a.ncols, a.nterms);
-                        },
-                        nullptr, nullptr, bar);
-      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
-    }
-    // ---- H: final residual + final norm -> LM head + arg-max
-    float bv[kMaxCols];
-    int bi[kMaxCols];
-#pragma unroll
-    for (int cc = 0; cc < kMaxCols; ++cc) { bv[cc] = -INFINITY; bi[cc] = 0x7fffffff; }
-    stream_gemv_phase(a, c, kSH, a.logits,
-                      [&](const float* g_pre, const float* g_post) {
-                        stream_prologue_resid(a, c, cta, a.fpart, a.down_slices, a.xres[0], a.xres[1], g_post, g_pre,
-                                              a.gmax_final);
-                      },
-                      bv, bi, bar);
-    {
-      float* sv = c.s.argbuf;
-      int* si = reinterpret_cast<int*>(c.s.argbuf + kDecThreads);
-      for (int col = 0; col < a.ncols; ++col) {
-        dec_sync();
-        sv[threadIdx.x] = bv[col];
-        si[threadIdx.x] = bi[col];
-        dec_sync();
-        for (int stp = kDecThreads / 2; stp > 0; stp >>= 1) {
-          if (threadIdx.x < stp) {
-            float ov = sv[threadIdx.x + stp];
-            int oi = si[threadIdx.x + stp];
-            if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
-              sv[threadIdx.x] = ov;
-              si[threadIdx.x] = oi;
-            }
-          }
+      if (ph == kSH) {       // CTA-level arg-max (lowest index wins ties), one slot per CTA
+        float* sv = c.s.argbuf;
+        int* si = reinterpret_cast<int*>(c.s.argbuf + kDecThreads);
+        for (int col = 0; col < a.ncols; ++col) {
           dec_sync();
-        }
-        if (threadIdx.x == 0) {
-          a.amax_val[(size_t)cta * a.ncols + col] = sv[0];
-          a.amax_idx[(size_t)cta * a.ncols + col] = si[0];
+          sv[threadIdx.x] = bv[col];
+          si[threadIdx.x] = bi[col];
+          dec_sync();
+          for (int stp = kDecThreads / 2; stp > 0; stp >>= 1) {
+            if (threadIdx.x < stp) {
+              float ov = sv[threadIdx.x + stp];
+              int oi = si[threadIdx.x + stp];
+              if (ov > sv[threadIdx.x] || (ov == sv[threadIdx.x] && oi < si[threadIdx.x])) {
+                sv[threadIdx.x] = ov;
+                si[threadIdx.x] = oi;
+              }
+            }
+            dec_sync();
+          }
+          if (threadIdx.x == 0) {
+            a.amax_val[(size_t)cta * a.ncols + col] = sv[0];
+            a.amax_idx[(size_t)cta * a.ncols + col] = si[0];
+          }
         }
       }
+      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
     }
-    grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
     if (cta == 0) phase_argmax(a, ncta);
     grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
   }
+}
+
+// Host-side selection of the instantiation for a model.
+inline const void* decode_stream_kernel_for(const ModelDims& d) {
+  const int G = d.hq / d.hkv;
+#define B2_PICK_G(T, HD)                                                                  \
+  (G == 1 ? (const void*)decode_stream_kernel<T, HD, 1>                                   \
+          : G == 2 ? (const void*)decode_stream_kernel<T, HD, 2> : (const void*)decode_stream_kernel<T, HD, 4>)
+#define B2_PICK_HD(T)                                                                     \
+  (d.hd == 32 ? B2_PICK_G(T, 32) : d.hd == 64 ? B2_PICK_G(T, 64) : d.hd == 128 ? B2_PICK_G(T, 128) : B2_PICK_G(T, 256))
+  return d.kv_dtype == 0 ? B2_PICK_HD(float) : B2_PICK_HD(__nv_bfloat16);
+#undef B2_PICK_HD
+#undef B2_PICK_G
 }
 
 }  // namespace b200lm

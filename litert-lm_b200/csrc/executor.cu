@@ -19,6 +19,7 @@
 #include "decode_stream.cuh"
 #include "model_host.h"
 #include "prefill_ops.cuh"
+#include "prefill_attn_tc.cuh"
 #include "runtime.h"
 
 namespace b200lm {
@@ -150,6 +151,13 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
     L.g_post_attn = fvec(p + "post_attn", d.d);
     L.g_pre_ffn = fvec(p + "pre_ffn", d.d);
     L.g_post_ffn = fvec(p + "post_ffn", d.d);
+    {
+      const float* gq = reinterpret_cast<const float*>(bytes(rec.need(p + "q_norm", 1)));
+      const float* gk = reinterpret_cast<const float*>(bytes(rec.need(p + "k_norm", 1)));
+      float mq = 0.f, mk = 0.f;
+      for (int k = 0; k < d.hd; ++k) { mq = std::max(mq, std::fabs(gq[k])); mk = std::max(mk, std::fabs(gk[k])); }
+      m->attn_bound.push_back(std::sqrt((float)d.hd) * mq * mk * 1.01f);
+    }
     L.g_q = fvec(p + "q_norm", d.hd);
     L.g_k = fvec(p + "k_norm", d.hd);
     L.is_global = d.is_global(i) ? 1 : 0;
@@ -212,6 +220,18 @@ CUtensorMap make_activation_map(const __nv_bfloat16* base, int rows, int cols) {
   cuuint32_t estr[2] = {1, 1};
   CUresult r = encode_tiled_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(base), dims,
                                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  B2_CHECK(r == CUDA_SUCCESS, kInternal, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
+  return tm;
+}
+
+// bf16 tensor of rank 2 or 3 (innermost dimension first), 128-byte swizzle.
+static CUtensorMap make_bf16_map(const void* base, int rank, const cuuint64_t* dims, const cuuint64_t* strides_bytes,
+                                 const cuuint32_t* box) {
+  CUtensorMap tm;
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = encode_tiled_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, (cuuint32_t)rank, const_cast<void*>(base), dims,
+                                 strides_bytes, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   B2_CHECK(r == CUDA_SUCCESS, kInternal, "cuTensorMapEncodeTiled failed: " + std::to_string((int)r));
   return tm;
@@ -301,11 +321,18 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   e->pages_per_seq = (d.max_ctx + kPage - 1) / kPage;
   size_t pool = (size_t)e->pages_per_seq * d.hkv * kPage * d.hd;
   e->kv_host.resize(d.n_layers);
+  // tensor-core prefill attention: head_dim 128 / 256, and every layer's score bound small enough
+  e->attn_tc = e->prefill_gemm == B200LM_GEMM_TCGEN05 && (d.hd == 128 || d.hd == 256);
+  for (float b : model->attn_bound) e->attn_tc = e->attn_tc && b <= kFaMaxBound;
   for (int i = 0; i < d.n_layers; ++i) {
     e->kv_host[i].k = e->alloc(pool * esz, true);
     e->kv_host[i].v = e->alloc(pool * esz, true);
     e->kv_host[i].k16 = nullptr;
     e->kv_host[i].v16 = nullptr;
+    if (e->attn_tc) {
+      if (d.kv_dtype == 0) e->kv_host[i].k16 = reinterpret_cast<__nv_bfloat16*>(e->alloc(pool * 2, true));
+      e->kv_host[i].v16 = reinterpret_cast<__nv_bfloat16*>(e->alloc(pool * 2, true));
+    }
   }
   LayerKv* kvd = reinterpret_cast<LayerKv*>(e->alloc(sizeof(LayerKv) * d.n_layers, false));
   B2_CUDA(cudaMemcpy(kvd, e->kv_host.data(), sizeof(LayerKv) * d.n_layers, cudaMemcpyHostToDevice));
@@ -381,9 +408,11 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
     if (ok) {
       e->stream_half = half;
       e->stream_smem = fixed + 2 * (size_t)half;
-      B2_CUDA(cudaFuncSetAttribute(decode_stream_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->stream_smem));
-      int occ = 0;
-      B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_stream_kernel, kStreamThreads, e->stream_smem));
+      const void* kfn = decode_stream_kernel_for(d);
+      B2_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->stream_smem));
+      cudaFuncAttributes fa;
+      B2_CUDA(cudaFuncGetAttributes(&fa, kfn));
+      int occ = (size_t)fa.maxThreadsPerBlock >= (size_t)kStreamThreads ? 1 : 0;
       ok = occ >= 1;
     }
     if (!ok) e->decode_mode = B200LM_DECODE_PHASE_KERNELS;
@@ -404,6 +433,32 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   e->pf_attn = reinterpret_cast<__nv_bfloat16*>(e->alloc(2 * tp * d.nq(), true));
   e->pf_act = reinterpret_cast<__nv_bfloat16*>(e->alloc(2 * tp * d.ffn, true));
   e->pf_parts = reinterpret_cast<float*>(e->alloc(sizeof(float) * 8 * tp * d.d, true));
+  if (e->attn_tc) {
+    const int G = d.group();
+    e->pf_q = reinterpret_cast<__nv_bfloat16*>(e->alloc(2 * tp * d.nq(), true));
+    {
+      cuuint64_t dims[3] = {(cuuint64_t)d.hd, (cuuint64_t)d.hq, (cuuint64_t)tp};
+      cuuint64_t str[2] = {(cuuint64_t)d.hd * 2, (cuuint64_t)d.nq() * 2};
+      cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(128 / G)};
+      e->tm_q = make_bf16_map(e->pf_q, 3, dims, str, box);
+    }
+    const cuuint64_t rows = (cuuint64_t)e->pages_per_seq * d.hkv * kPage;
+    for (int i = 0; i < d.n_layers; ++i) {
+      const void* kbase = d.kv_dtype == 0 ? (const void*)e->kv_host[i].k16 : (const void*)e->kv_host[i].k;
+      cuuint64_t kd[2] = {(cuuint64_t)d.hd, rows};
+      cuuint64_t ks[1] = {(cuuint64_t)d.hd * 2};
+      cuuint32_t kb[2] = {64, (cuuint32_t)kFaBN};
+      e->tm_k.push_back(make_bf16_map(kbase, 2, kd, ks, kb));
+      cuuint64_t vd[2] = {(cuuint64_t)kPage, (cuuint64_t)e->pages_per_seq * d.hkv * d.hd};
+      cuuint64_t vs[1] = {(cuuint64_t)kPage * 2};
+      cuuint32_t vb[2] = {(cuuint32_t)kFaBN, (cuuint32_t)d.hd};
+      e->tm_vt.push_back(make_bf16_map(e->kv_host[i].v16, 2, vd, vs, vb));
+    }
+    if (d.hd == 256)
+      B2_CUDA(cudaFuncSetAttribute(flash_prefill_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<256>::kTotal));
+    else
+      B2_CUDA(cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<128>::kTotal));
+  }
   if (e->prefill_gemm == B200LM_GEMM_TCGEN05) {
     e->tm_h = make_activation_map(e->pf_h, (int)tp, d.d);
     e->tm_attn = make_activation_map(e->pf_attn, (int)tp, d.nq());
@@ -440,8 +495,10 @@ void Executor::check_device_error(const char* where) {
 
 template <typename T>
 static void launch_kv_append(cudaStream_t st, const ModelDims& d, int T_, const float* qkv, int pos0, const int* pt,
-                             const LayerWeights& L, const float* c, const float* s, const LayerKv& kv) {
-  pf_kv_append_kernel<T><<<T_, kPfThreads, 0, st>>>(d, qkv, pos0, pt, L.g_k, c, s, kv);
+                             const LayerWeights& L, const float* c, const float* s, const LayerKv& kv,
+                             __nv_bfloat16* qout) {
+  const int threads = qout ? 256 : kPfThreads;      // more heads per token when queries are prepared too
+  pf_kv_append_kernel<T><<<T_, threads, 0, st>>>(d, qkv, pos0, pt, L.g_k, c, s, kv, L.g_q, qout);
 }
 
 void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
@@ -470,9 +527,18 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
     const float* sinT = model->rope_sin[L.is_global];
     launch_gemm(stream, mode, tm_h, pf_h, L.wqkv, L.sqkv, Gm.wqkv, Gm.sqkv, T, d.nqkv(), d.d, 1, false, pf_qkv,
                 nullptr, err, &launches);
-    if (d.kv_dtype == 0) launch_kv_append<float>(stream, d, T, pf_qkv, start, page_table_dev, L, cosT, sinT, kv_host[li]);
-    else launch_kv_append<__nv_bfloat16>(stream, d, T, pf_qkv, start, page_table_dev, L, cosT, sinT, kv_host[li]);
+    __nv_bfloat16* qout = attn_tc ? pf_q : nullptr;
+    if (d.kv_dtype == 0) launch_kv_append<float>(stream, d, T, pf_qkv, start, page_table_dev, L, cosT, sinT, kv_host[li], qout);
+    else launch_kv_append<__nv_bfloat16>(stream, d, T, pf_qkv, start, page_table_dev, L, cosT, sinT, kv_host[li], qout);
     ++launches;
+    if (attn_tc) {
+      FaArgs fa{T, start, d.hq, d.hkv, d.window, L.is_global, page_table_dev, pf_attn, model->attn_bound[li], err};
+      const int TT = 128 / d.group();
+      dim3 grid((T + TT - 1) / TT, d.hkv);
+      if (d.hd == 256) flash_prefill_tc_kernel<256><<<grid, kFaThreads, FaSmem<256>::kTotal, stream>>>(tm_q, tm_k[li], tm_vt[li], fa);
+      else flash_prefill_tc_kernel<128><<<grid, kFaThreads, FaSmem<128>::kTotal, stream>>>(tm_q, tm_k[li], tm_vt[li], fa);
+      ++launches;
+    } else {
     AttnJob j;
     memset(&j, 0, sizeof j);
     j.qkv = pf_qkv;
@@ -493,6 +559,7 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
     j.err = err;
     pf_attn_kernel<<<T * d.hkv, 256, attn_smem, stream>>>(d, j);
     ++launches;
+    }
     int ks_o = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(mt * ((d.d + kGemmBN - 1) / kGemmBN), d.nq() / 64, n_sms) : 1;
     launch_gemm(stream, mode, tm_attn, pf_attn, L.wo, L.so, Gm.wo, Gm.so, T, d.d, d.nq(), ks_o, false, pf_parts,
                 nullptr, err, &launches);
@@ -571,7 +638,7 @@ void Executor::launch_decode_steps(int nsteps) {
     if (decode_mode == B200LM_DECODE_PERSISTENT) {
       int half = stream_half;
       void* params[] = {&a, &nsteps, &epoch0, &half};
-      B2_CUDA(cudaLaunchCooperativeKernel((void*)decode_stream_kernel, dim3(ncta), dim3(kStreamThreads), params,
+      B2_CUDA(cudaLaunchCooperativeKernel(decode_stream_kernel_for(d), dim3(ncta), dim3(kStreamThreads), params,
                                           stream_smem, stream));
     } else {
       void* params[] = {&a, &nsteps, &epoch0};

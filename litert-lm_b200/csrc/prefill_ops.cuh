@@ -95,13 +95,16 @@ pf_resid_norm_kernel(const float* __restrict__ parts, int nparts, size_t part_st
     h[(size_t)t * d + i] = __float2bfloat16(pf_sm[i] * r2 * g_pre[i]);
 }
 
-// K-RMSNorm + RoPE on the new keys, then K and V rows into the paged cache
-// (and its bf16 shadow).  One CTA per token; one warp per kv head (looped).
+// K-RMSNorm + RoPE on the new keys, then K and V rows into the paged cache (and
+// the bf16 operands of the tensor-core attention); with qout, also Q-RMSNorm +
+// RoPE + 1/sqrt(hd) on the query heads into a bf16 [T][hq][hd] buffer.  One CTA
+// per token; one warp per head (looped).
 template <typename T>
-__global__ void __launch_bounds__(kPfThreads)
+__global__ void __launch_bounds__(256)
 pf_kv_append_kernel(ModelDims dm, const float* __restrict__ qkv, int pos0,
                     const int* __restrict__ page_table, const float* __restrict__ g_k,
-                    const float* __restrict__ cosT, const float* __restrict__ sinT, LayerKv kv) {
+                    const float* __restrict__ cosT, const float* __restrict__ sinT, LayerKv kv,
+                    const float* __restrict__ g_q, __nv_bfloat16* __restrict__ qout) {
   const int t = blockIdx.x, pos = pos0 + t;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int hd = dm.hd, half = hd / 2;
@@ -109,7 +112,25 @@ pf_kv_append_kernel(ModelDims dm, const float* __restrict__ qkv, int pos0,
   const int page = page_table[pos / kPage], slot = pos % kPage;
   T* kbase = reinterpret_cast<T*>(kv.k);
   T* vbase = reinterpret_cast<T*>(kv.v);
-  for (int kh = warp; kh < dm.hkv; kh += nwarps) {
+  const int nheads = dm.hkv + (qout ? dm.hq : 0);
+  for (int h = warp; h < nheads; h += nwarps) {
+    if (h >= dm.hkv) {           // a query head
+      const int qh = h - dm.hkv;
+      const float* qs = row + (size_t)qh * hd;
+      float ss = 0.f;
+      for (int e = lane; e < hd; e += 32) ss += qs[e] * qs[e];
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / (float)hd + dm.eps) * rsqrtf((float)hd);
+      __nv_bfloat16* dst = qout + ((size_t)t * dm.hq + qh) * hd;
+      for (int e = lane; e < half; e += 32) {
+        float a0 = qs[e] * r * g_q[e], b0 = qs[e + half] * r * g_q[e + half];
+        float cs = cosT[(size_t)pos * half + e], sn = sinT[(size_t)pos * half + e];
+        dst[e] = __float2bfloat16(a0 * cs - b0 * sn);
+        dst[e + half] = __float2bfloat16(b0 * cs + a0 * sn);
+      }
+      continue;
+    }
+    const int kh = h;
     const float* ks = row + dm.nq() + (size_t)kh * hd;
     const float* vs = row + dm.nq() + dm.nkv() + (size_t)kh * hd;
     size_t off = (((size_t)page * dm.hkv + kh) * kPage + slot) * hd;
@@ -125,13 +146,15 @@ pf_kv_append_kernel(ModelDims dm, const float* __restrict__ qkv, int pos0,
       if constexpr (sizeof(T) == 4) {
         kbase[off + e] = k0; kbase[off + e + half] = k1;
         vbase[off + e] = v0; vbase[off + e + half] = v1;
-        if (kv.k16) {
-          kv.k16[off + e] = __float2bfloat16(k0); kv.k16[off + e + half] = __float2bfloat16(k1);
-          kv.v16[off + e] = __float2bfloat16(v0); kv.v16[off + e + half] = __float2bfloat16(v1);
-        }
+        if (kv.k16) { kv.k16[off + e] = __float2bfloat16(k0); kv.k16[off + e + half] = __float2bfloat16(k1); }
       } else {
         kbase[off + e] = __float2bfloat16(k0); kbase[off + e + half] = __float2bfloat16(k1);
         vbase[off + e] = __float2bfloat16(v0); vbase[off + e + half] = __float2bfloat16(v1);
+      }
+      if (kv.v16) {
+        size_t vt = (((size_t)page * dm.hkv + kh) * hd + e) * kPage + slot;
+        kv.v16[vt] = __float2bfloat16(v0);
+        kv.v16[vt + (size_t)half * kPage] = __float2bfloat16(v1);
       }
     }
   }

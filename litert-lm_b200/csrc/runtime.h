@@ -34,6 +34,7 @@ struct Model {
   const float* rope_sin[2] = {nullptr, nullptr};
   std::vector<LayerWeights> layers_host;
   std::vector<LayerGemmWeights> gemm_host;
+  std::vector<float> attn_bound;     // per layer: sqrt(hd) max|g_q| max|g_k| >= any |q.k| / sqrt(hd)
   const LayerWeights* layers_dev = nullptr;
   std::vector<void*> allocations;
 
@@ -108,6 +109,10 @@ class Executor {
   __nv_bfloat16* pf_act = nullptr;
   float* pf_parts = nullptr;
   CUtensorMap tm_h{}, tm_attn{}, tm_act{};
+  bool attn_tc = false;             // tensor-core prefill attention in use
+  __nv_bfloat16* pf_q = nullptr;    // [t_pad][hq][hd] normalised, rotated, scaled queries
+  CUtensorMap tm_q{};
+  std::vector<CUtensorMap> tm_k, tm_vt;   // per layer
   // pinned staging
   void* pinned = nullptr;
   float* pin_logits = nullptr;

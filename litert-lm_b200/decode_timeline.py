@@ -90,6 +90,10 @@ def main() -> None:
                 ok = (p[:, :, lo] > 0) & (p[:, :, hi] > 0)
                 d = np.where(ok, (p[:, :, hi] - p[:, :, lo]) * us, np.nan)
                 seg.append((labels[k], float(np.nanmean(d)) if ok.any() else float("nan")))
+            for lo, hi, nm in ((1, 2, "loads+sums"), (2, 7, "block reduce"), (7, 3, "quantize")):
+                ok = (p[:, :, lo] > 0) & (p[:, :, hi] > 0)
+                if ok.any():
+                    seg.append((nm, float(np.nanmean(np.where(ok, (p[:, :, hi] - p[:, :, lo]) * us, np.nan)))))
             arr = stamps[idx, :, 0].astype(np.float64)
             lastp = np.where(p[:, :, 6] > 0, (arr - p[:, :, 6]) * us, np.nan)
             seg.append(("end->arrive", float(np.nanmean(lastp)) if np.isfinite(lastp).any() else float("nan")))
