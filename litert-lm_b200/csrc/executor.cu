@@ -19,6 +19,7 @@
 #include "decode_stream.cuh"
 #include "model_host.h"
 #include "prefill_ops.cuh"
+#include "prefill_gemm_ts.cuh"
 #include "prefill_attn_tc.cuh"
 #include "runtime.h"
 
@@ -165,12 +166,12 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
       upload_w4g(*m, bytes(eqkv), sqkv, d.nqkv(), d.d, &Gm.wqkv, &Gm.sqkv);
       upload_w4g(*m, bytes(eo), so, d.d, d.nq(), &Gm.wo, &Gm.so);
       upload_w4g(*m, bytes(ed), sd, d.d, d.ffn, &Gm.wdown, &Gm.sdown);
-      // 128-row tiles: 64 gate rows then the matching 64 up rows
+      // 128-row tiles of 64 ffn features: gate row of a feature, then its up row
       int64_t tiles = ffn / 64;
       std::vector<uint32_t> buf((size_t)tiles * 128 * d.d / 8);
       auto map = [ffn](int64_t r) {
         int64_t j = r / 128, c = r % 128;
-        return c < 64 ? j * 64 + c : ffn + j * 64 + (c - 64);
+        return (c & 1 ? ffn : (int64_t)0) + j * 64 + (c >> 1);
       };
       repack_w4g(gu.data(), tiles, d.d, map, buf.data());
       Gm.wgu = reinterpret_cast<const uint8_t*>(upload(*m, buf.data(), buf.size()));
@@ -237,13 +238,21 @@ static CUtensorMap make_bf16_map(const void* base, int rank, const cuuint64_t* d
   return tm;
 }
 
-int pick_ksplit(int tiles, int KB, int sms) {
+// Split-K factor for a GEMM of `n_tiles` weight-row tiles over T tokens with KB
+// 64-wide k blocks: the smallest divisor of KB (at least 4 k blocks per split,
+// at most 8 splits) whose work units fill 90 % of the last round over the SMs,
+// else the divisor that fills it best.
+int pick_ksplit(int T, int n_tiles, int KB, int sms) {
+  const int tiles = n_tiles * ((T + kTsTok - 1) / kTsTok);
   int best = 1;
+  double best_eff = 0.0;
   for (int s = 1; s <= 8; ++s) {
     if (KB % s) continue;
-    if (KB / s < 4) break;
-    best = s;
-    if (tiles * s >= 2 * sms) break;
+    if (s > 1 && KB / s < 4) break;
+    const int units = tiles * s;
+    const double eff = (double)units / ((double)((units + sms - 1) / sms) * sms);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best = s; }
+    if (eff >= 0.9) break;
   }
   return best;
 }
@@ -254,14 +263,20 @@ void launch_gemm(cudaStream_t st, int mode, const CUtensorMap& a_map, const __nv
                  int ksplit, bool geglu, float* outF, __nv_bfloat16* outB, int* err, int64_t* launches) {
   if (mode == B200LM_GEMM_TCGEN05) {
     GemmArgs g{w4g, s4g, T, N, K, ksplit, outF, outB, err};
-    dim3 grid((N + kGemmBN - 1) / kGemmBN, (T + kGemmBM - 1) / kGemmBM, ksplit);
-    if (geglu) {
-      B2_CUDA(cudaFuncSetAttribute(gemm_w4_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
-      gemm_w4_tc_kernel<1><<<grid, kGemmThreads, kGemmSmem, st>>>(a_map, g);
-    } else {
-      B2_CUDA(cudaFuncSetAttribute(gemm_w4_tc_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kGemmSmem));
-      gemm_w4_tc_kernel<0><<<grid, kGemmThreads, kGemmSmem, st>>>(a_map, g);
+    static int sms_of[64] = {0};              // per device: SM count, set once together with the kernel attributes
+    int dev = 0;
+    B2_CUDA(cudaGetDevice(&dev));
+    B2_CHECK(dev >= 0 && dev < 64, kInternal, "device ordinal out of range");
+    if (!sms_of[dev]) {
+      B2_CUDA(cudaFuncSetAttribute(gemm_w4_ts_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsSmem));
+      B2_CUDA(cudaFuncSetAttribute(gemm_w4_ts_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsSmem));
+      B2_CUDA(cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev));
     }
+    const int sms = sms_of[dev];
+    const int total = ((N + kTsRows - 1) / kTsRows) * ((T + kTsTok - 1) / kTsTok) * ksplit;
+    const int grid = total < sms ? total : sms;
+    if (geglu) gemm_w4_ts_kernel<1><<<grid, kTsThreads, kTsSmem, st>>>(a_map, g);
+    else gemm_w4_ts_kernel<0><<<grid, kTsThreads, kTsSmem, st>>>(a_map, g);
   } else {
     B2_CHECK(ksplit == 1, kInternal, "the check GEMM does not split K");
     dim3 grid(geglu ? N / 32 : N / 16, (T + 7) / 8);
@@ -493,12 +508,29 @@ void Executor::check_device_error(const char* where) {
 
 // ------------------------------------------------------------------- prefill
 
+// x += rmsnorm(sum of split-K partials) * g_post ; h = bf16(rmsnorm(x) * g_pre)
+static void launch_resid_norm(cudaStream_t st, const float* parts, int nparts, int T, const ModelDims& d,
+                              const float* g_post, const float* g_pre, float* xres, __nv_bfloat16* h) {
+  const int per_lane = (d.d / 4 + 31) / 32;
+  const size_t stride = (size_t)T * d.d;
+  const int grid = (T + 7) / 8;
+  if (per_lane <= 4)
+    pf_resid_norm_warp_kernel<4><<<grid, 256, 0, st>>>(parts, nparts, stride, d.d, T, d.eps, g_post, g_pre, xres, h);
+  else if (per_lane <= 12)
+    pf_resid_norm_warp_kernel<12><<<grid, 256, 0, st>>>(parts, nparts, stride, d.d, T, d.eps, g_post, g_pre, xres, h);
+  else
+    pf_resid_norm_kernel<<<T, kPfThreads, sizeof(float) * d.d, st>>>(parts, nparts, stride, d.d, d.eps, g_post, g_pre,
+                                                                    xres, h);
+}
+
 template <typename T>
-static void launch_kv_append(cudaStream_t st, const ModelDims& d, int T_, const float* qkv, int pos0, const int* pt,
+static void launch_kv_append(cudaStream_t st, const ModelDims& d, int T_, const float* qkv, int nparts, int pos0, const int* pt,
                              const LayerWeights& L, const float* c, const float* s, const LayerKv& kv,
                              __nv_bfloat16* qout) {
   const int threads = qout ? 256 : kPfThreads;      // more heads per token when queries are prepared too
-  pf_kv_append_kernel<T><<<T_, threads, 0, st>>>(d, qkv, pos0, pt, L.g_k, c, s, kv, L.g_q, qout);
+  const size_t smem = nparts > 1 ? sizeof(float) * d.nqkv() : 0;
+  pf_kv_append_kernel<T><<<T_, threads, smem, st>>>(d, qkv, nparts, (size_t)T_ * d.nqkv(), pos0, pt, L.g_k, c, s, kv,
+                                                    L.g_q, qout);
 }
 
 void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
@@ -517,7 +549,6 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
                                                         pf_xres, pf_h, err);
   ++launches;
   const int mode = prefill_gemm;
-  const int mt = (T + kGemmBM - 1) / kGemmBM;
   const size_t attn_smem = sizeof(float) * ((size_t)(d.group() + 2) * d.hd + (size_t)8 * d.group() * (d.hd + 2));
   B2_CUDA(cudaFuncSetAttribute(pf_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem));
   for (int li = 0; li < d.n_layers; ++li) {
@@ -525,11 +556,19 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
     const LayerGemmWeights& Gm = model->gemm_host[li];
     const float* cosT = model->rope_cos[L.is_global];
     const float* sinT = model->rope_sin[L.is_global];
-    launch_gemm(stream, mode, tm_h, pf_h, L.wqkv, L.sqkv, Gm.wqkv, Gm.sqkv, T, d.nqkv(), d.d, 1, false, pf_qkv,
+    // split-K partials of the QKV rows go to the partials buffer (8 x d floats per token) and are summed by
+    // the append kernel; the CUDA-core attention reads whole rows, so it keeps one split
+    int ks_q = 1;
+    if (mode == B200LM_GEMM_TCGEN05 && attn_tc) {
+      ks_q = pick_ksplit(T, (d.nqkv() + kTsRows - 1) / kTsRows, d.d / 64, n_sms);
+      if ((size_t)ks_q * d.nqkv() > (size_t)8 * d.d) ks_q = 1;
+    }
+    float* qkv_buf = ks_q > 1 ? pf_parts : pf_qkv;
+    launch_gemm(stream, mode, tm_h, pf_h, L.wqkv, L.sqkv, Gm.wqkv, Gm.sqkv, T, d.nqkv(), d.d, ks_q, false, qkv_buf,
                 nullptr, err, &launches);
     __nv_bfloat16* qout = attn_tc ? pf_q : nullptr;
-    if (d.kv_dtype == 0) launch_kv_append<float>(stream, d, T, pf_qkv, start, page_table_dev, L, cosT, sinT, kv_host[li], qout);
-    else launch_kv_append<__nv_bfloat16>(stream, d, T, pf_qkv, start, page_table_dev, L, cosT, sinT, kv_host[li], qout);
+    if (d.kv_dtype == 0) launch_kv_append<float>(stream, d, T, qkv_buf, ks_q, start, page_table_dev, L, cosT, sinT, kv_host[li], qout);
+    else launch_kv_append<__nv_bfloat16>(stream, d, T, qkv_buf, ks_q, start, page_table_dev, L, cosT, sinT, kv_host[li], qout);
     ++launches;
     if (attn_tc) {
       FaArgs fa{T, start, d.hq, d.hkv, d.window, L.is_global, page_table_dev, pf_attn, model->attn_bound[li], err};
@@ -560,20 +599,18 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
     pf_attn_kernel<<<T * d.hkv, 256, attn_smem, stream>>>(d, j);
     ++launches;
     }
-    int ks_o = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(mt * ((d.d + kGemmBN - 1) / kGemmBN), d.nq() / 64, n_sms) : 1;
+    int ks_o = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(T, (d.d + kTsRows - 1) / kTsRows, d.nq() / 64, n_sms) : 1;
     launch_gemm(stream, mode, tm_attn, pf_attn, L.wo, L.so, Gm.wo, Gm.so, T, d.d, d.nq(), ks_o, false, pf_parts,
                 nullptr, err, &launches);
-    pf_resid_norm_kernel<<<T, kPfThreads, sm_d, stream>>>(pf_parts, ks_o, (size_t)T * d.d, d.d, d.eps, L.g_post_attn,
-                                                          L.g_pre_ffn, pf_xres, pf_h);
+    launch_resid_norm(stream, pf_parts, ks_o, T, d, L.g_post_attn, L.g_pre_ffn, pf_xres, pf_h);
     ++launches;
     launch_gemm(stream, mode, tm_h, pf_h, L.wgu, L.sgu, Gm.wgu, Gm.sgu, T, 2 * d.ffn, d.d, 1, true, nullptr, pf_act,
                 err, &launches);
-    int ks_d = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(mt * ((d.d + kGemmBN - 1) / kGemmBN), d.ffn / 64, n_sms) : 1;
+    int ks_d = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(T, (d.d + kTsRows - 1) / kTsRows, d.ffn / 64, n_sms) : 1;
     launch_gemm(stream, mode, tm_act, pf_act, L.wdown, L.sdown, Gm.wdown, Gm.sdown, T, d.d, d.ffn, ks_d, false,
                 pf_parts, nullptr, err, &launches);
     const float* g_next = li + 1 < d.n_layers ? model->layers_host[li + 1].g_pre_attn : nullptr;
-    pf_resid_norm_kernel<<<T, kPfThreads, sm_d, stream>>>(pf_parts, ks_d, (size_t)T * d.d, d.d, d.eps, L.g_post_ffn,
-                                                          g_next, pf_xres, pf_h);
+    launch_resid_norm(stream, pf_parts, ks_d, T, d, L.g_post_ffn, g_next, pf_xres, pf_h);
     ++launches;
   }
   B2_CUDA(cudaGetLastError());

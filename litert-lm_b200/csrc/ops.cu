@@ -232,7 +232,7 @@ static void run_gemm_common(int device, int mode, const uint8_t* packed_rows, co
   std::vector<float> sg((size_t)tiles * 128, 1.0f);
   if (geglu) {
     auto mapt = [ffn](int64_t r) { int64_t tile = r / 16, pair = tile / 2; return (tile & 1 ? ffn : (int64_t)0) + pair * 16 + (r % 16); };
-    auto mapg = [ffn](int64_t r) { int64_t j = r / 128, c = r % 128; return c < 64 ? j * 64 + c : ffn + j * 64 + (c - 64); };
+    auto mapg = [ffn](int64_t r) { int64_t j = r / 128, c = r % 128; return (c & 1 ? ffn : (int64_t)0) + j * 64 + (c >> 1); };
     repack_w4t(packed_rows, n, k, mapt, t4.data());
     repack_w4g(packed_rows, tiles, k, mapg, g4.data());
     for (int64_t r = 0; r < n; ++r) st[r] = scales[mapt(r)];

@@ -95,20 +95,98 @@ pf_resid_norm_kernel(const float* __restrict__ parts, int nparts, size_t part_st
     h[(size_t)t * d + i] = __float2bfloat16(pf_sm[i] * r2 * g_pre[i]);
 }
 
+// Same as pf_resid_norm_kernel, one WARP per token: the token's row lives in
+// registers (MAXV float4 per lane), sums are warp shuffles, every load is a
+// 16-byte load and the loads of one partial are independent.
+template <int MAXV>
+__global__ void __launch_bounds__(256)
+pf_resid_norm_warp_kernel(const float* __restrict__ parts, int nparts, size_t part_stride, int d, int T, float eps,
+                          const float* __restrict__ g_post, const float* __restrict__ g_pre,
+                          float* __restrict__ xres, __nv_bfloat16* __restrict__ h) {
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= T) return;
+  const int d4 = d / 4;
+  float4 f[MAXV];
+  float ss = 0.f;
+#pragma unroll
+  for (int u = 0; u < MAXV; ++u) f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int p = 0; p < nparts; ++p) {
+    const float4* src = reinterpret_cast<const float4*>(parts + (size_t)p * part_stride + (size_t)t * d);
+#pragma unroll
+    for (int u = 0; u < MAXV; ++u) {
+      const int i = lane + 32 * u;
+      if (i < d4) {
+        float4 v = src[i];
+        f[u].x += v.x; f[u].y += v.y; f[u].z += v.z; f[u].w += v.w;
+      }
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < MAXV; ++u) ss += f[u].x * f[u].x + f[u].y * f[u].y + f[u].z * f[u].z + f[u].w * f[u].w;
+  ss = warp_sum(ss);
+  const float r = rsqrtf(ss / (float)d + eps);
+  float4* xr = reinterpret_cast<float4*>(xres + (size_t)t * d);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int u = 0; u < MAXV; ++u) {
+    const int i = lane + 32 * u;
+    if (i < d4) {
+      float4 x = xr[i], gp = reinterpret_cast<const float4*>(g_post)[i];
+      x.x += f[u].x * r * gp.x; x.y += f[u].y * r * gp.y; x.z += f[u].z * r * gp.z; x.w += f[u].w * r * gp.w;
+      xr[i] = x;
+      f[u] = x;
+      ss2 += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+    }
+  }
+  if (g_pre == nullptr) return;
+  ss2 = warp_sum(ss2);
+  const float r2 = rsqrtf(ss2 / (float)d + eps);
+#pragma unroll
+  for (int u = 0; u < MAXV; ++u) {
+    const int i = lane + 32 * u;
+    if (i < d4) {
+      float4 gq = reinterpret_cast<const float4*>(g_pre)[i];
+      __nv_bfloat162 a = __floats2bfloat162_rn(f[u].x * r2 * gq.x, f[u].y * r2 * gq.y);
+      __nv_bfloat162 b = __floats2bfloat162_rn(f[u].z * r2 * gq.z, f[u].w * r2 * gq.w);
+      uint2 w;
+      w.x = *reinterpret_cast<uint32_t*>(&a);
+      w.y = *reinterpret_cast<uint32_t*>(&b);
+      reinterpret_cast<uint2*>(h + (size_t)t * d)[i] = w;
+    }
+  }
+}
+
 // K-RMSNorm + RoPE on the new keys, then K and V rows into the paged cache (and
 // the bf16 operands of the tensor-core attention); with qout, also Q-RMSNorm +
 // RoPE + 1/sqrt(hd) on the query heads into a bf16 [T][hq][hd] buffer.  One CTA
-// per token; one warp per head (looped).
+// per token; one warp per head (looped).  The QKV row may arrive as `nparts`
+// split-K partial sums `part_stride` floats apart; they are added into shared
+// memory (nqkv floats of dynamic shared memory) first.
 template <typename T>
 __global__ void __launch_bounds__(256)
-pf_kv_append_kernel(ModelDims dm, const float* __restrict__ qkv, int pos0,
+pf_kv_append_kernel(ModelDims dm, const float* __restrict__ qkv, int nparts, size_t part_stride, int pos0,
                     const int* __restrict__ page_table, const float* __restrict__ g_k,
                     const float* __restrict__ cosT, const float* __restrict__ sinT, LayerKv kv,
                     const float* __restrict__ g_q, __nv_bfloat16* __restrict__ qout) {
   const int t = blockIdx.x, pos = pos0 + t;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
   const int hd = dm.hd, half = hd / 2;
+  extern __shared__ __align__(16) float kv_row[];
   const float* row = qkv + (size_t)t * dm.nqkv();
+  if (nparts > 1) {
+    const int n4 = dm.nqkv() / 4;
+    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
+      float4 a = reinterpret_cast<const float4*>(row)[i];
+      for (int p = 1; p < nparts; ++p) {
+        float4 b = reinterpret_cast<const float4*>(row + p * part_stride)[i];
+        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+      }
+      reinterpret_cast<float4*>(kv_row)[i] = a;
+    }
+    __syncthreads();
+    row = kv_row;
+  }
   const int page = page_table[pos / kPage], slot = pos % kPage;
   T* kbase = reinterpret_cast<T*>(kv.k);
   T* vbase = reinterpret_cast<T*>(kv.v);
@@ -307,13 +385,9 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 
 // ------------------------------------------------------ int4 tensor-core GEMM
 
-constexpr int kGemmBM = 128, kGemmBN = 128, kGemmBK = 64, kGemmStages = 3;
-constexpr int kGemmDeqWarps = 8;
-constexpr int kGemmThreads = 64 + 32 * kGemmDeqWarps;   // warp 0 loads, warp 1 issues MMA
-constexpr int kGemmStageA = kGemmBM * kGemmBK * 2;      // 16384
-constexpr int kGemmStageB = kGemmBN * kGemmBK * 2;      // 16384
-constexpr int kGemmStageQ = kGemmBN * kGemmBK / 2;      // 4096
-constexpr int kGemmSmem = kGemmStages * (kGemmStageA + kGemmStageB + kGemmStageQ) + 1024 + 256;
+constexpr int kGemmBM = 128;                      // activation rows are padded to this
+constexpr int kGemmBK = 64;                       // k block: one 128-byte swizzled row of bf16
+constexpr int kGemmStageQ = 128 * kGemmBK / 2;    // one int4 weight block: 128 rows x 32 bytes
 
 // Weight tiles ("W4G"): [n_tile][k_block] blocks of 128 rows x 32 bytes; a
 // 32-bit word holds 8 consecutive k of one row as nibbles ordered
@@ -322,176 +396,19 @@ struct GemmArgs {
   const uint8_t* w;        // W4G tiles
   const float* wscale;     // per weight row, in tile order, padded to the tile grid
   int T, N, K;             // N = logical output columns (unpadded)
-  int ksplit;              // grid.z; partial outputs [ksplit][T][N]
+  int ksplit;              // K splits; partial outputs [ksplit][T][N]
   float* outF;             // epilogue 0
   __nv_bfloat16* outB;     // epilogue 1 (GeGLU): [T][N/2]
   int* err;
+#ifdef B2_GEMM_TRACE
+  long long* trace;        // development builds only: clock stamps of the first and the last CTA
+#endif
 };
 
-template <int EPI>
-__global__ void __launch_bounds__(kGemmThreads, 2)
-gemm_w4_tc_kernel(const __grid_constant__ CUtensorMap tmA, GemmArgs g) {
-  extern __shared__ unsigned char gsm_raw[];
-  unsigned char* gsm = reinterpret_cast<unsigned char*>(((uintptr_t)gsm_raw + 1023) & ~(uintptr_t)1023);
-  unsigned char* sA = gsm;
-  unsigned char* sB = gsm + kGemmStages * kGemmStageA;
-  unsigned char* sQ = sB + kGemmStages * kGemmStageB;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + kGemmStages * kGemmStageQ);
-  uint64_t* full_bar = bars;                       // [stages] TMA bytes landed
-  uint64_t* deq_bar = bars + kGemmStages;          // [stages] bf16 weight tile written
-  uint64_t* empty_bar = bars + 2 * kGemmStages;    // [stages] MMA finished with the stage
-  uint64_t* acc_bar = bars + 3 * kGemmStages;      // accumulator complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 3 * kGemmStages + 1);
-
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_tile = blockIdx.x, m_tile = blockIdx.y, ks = blockIdx.z;
-  const int KB = g.K / kGemmBK;
-  const int kb_per = KB / g.ksplit;
-  const int kb0 = ks * kb_per;
-  const int nkb = kb_per;
-
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < kGemmStages; ++s) {
-      mbar_init(&full_bar[s], 1);
-      mbar_init(&deq_bar[s], kGemmDeqWarps);
-      mbar_init(&empty_bar[s], 1);
-    }
-    mbar_init(acc_bar, 1);
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  if (warp == 1) tmem_alloc(tmem_slot, kGemmBN);
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_acc = *tmem_slot;
-
-  if (warp == 0) {
-    if (lane == 0) {
-      const uint8_t* wtile = g.w + ((size_t)n_tile * KB + kb0) * kGemmStageQ;
-      for (int kb = 0; kb < nkb; ++kb) {
-        int s = kb % kGemmStages, n = kb / kGemmStages;
-        if (n > 0 && !mbar_wait(&empty_bar[s], (n - 1) & 1, g.err)) break;
-        mbar_arrive_expect_tx(&full_bar[s], kGemmStageA + kGemmStageQ);
-        tma_load_2d(sA + s * kGemmStageA, &tmA, (kb0 + kb) * kGemmBK, m_tile * kGemmBM, &full_bar[s]);
-        bulk_load_1d(sQ + s * kGemmStageQ, wtile + (size_t)kb * kGemmStageQ, kGemmStageQ, &full_bar[s]);
-      }
-    }
-  } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc = umma_idesc_bf16(kGemmBM, kGemmBN);
-      bool ok = true;
-      for (int kb = 0; kb < nkb && ok; ++kb) {
-        int s = kb % kGemmStages, n = kb / kGemmStages;
-        ok = mbar_wait(&full_bar[s], n & 1, g.err) && mbar_wait(&deq_bar[s], n & 1, g.err);
-        if (!ok) break;
-        tc_fence_after();
-        uint64_t ad = umma_desc_sw128(smem_u32(sA + s * kGemmStageA));
-        uint64_t bd = umma_desc_sw128(smem_u32(sB + s * kGemmStageB));
-#pragma unroll
-        for (int k = 0; k < kGemmBK / 16; ++k)   // 16 bf16 = 32 bytes along K per MMA
-          umma_bf16(tmem_acc, ad + (uint64_t)(k * 2), bd + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
-        umma_commit(&empty_bar[s]);
-      }
-      umma_commit(acc_bar);
-    }
-  } else {
-    // ---- int4 -> bf16 expansion into the swizzled B tile
-    const int dt = threadIdx.x - 64;            // 0..255
-    const int row = dt >> 1, hrow = dt & 1;     // half a row (32 k) per thread
-    bool ok = true;
-    for (int kb = 0; kb < nkb && ok; ++kb) {
-      int s = kb % kGemmStages, n = kb / kGemmStages;
-      ok = mbar_wait(&full_bar[s], n & 1, g.err);
-      if (ok && n > 0) ok = mbar_wait(&empty_bar[s], (n - 1) & 1, g.err);
-      if (!ok) break;
-      const uint4 q = *reinterpret_cast<const uint4*>(sQ + s * kGemmStageQ + row * 32 + hrow * 16);
-      const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
-      unsigned char* brow = sB + s * kGemmStageB + row * 128;
-      const __nv_bfloat162 bias = __float2bfloat162_rn(136.0f);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        uint32_t w = qw[j];
-        uint32_t r[4];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          uint32_t v = ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;   // bf16(128 + nibble) pairs
-          __nv_bfloat162 h = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&v), bias);
-          r[i] = *reinterpret_cast<uint32_t*>(&h);
-        }
-        int chunk = (hrow * 4 + j) ^ (row & 7);
-        *reinterpret_cast<uint4*>(brow + chunk * 16) = make_uint4(r[0], r[1], r[2], r[3]);
-      }
-      fence_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&deq_bar[s]);
-    }
-    // ---- epilogue: TMEM -> registers -> global
-    if (mbar_wait(acc_bar, 0, g.err)) {
-      tc_fence_after();
-      const int quarter = warp & 3;               // TMEM lanes this warp may read
-      const int second = (warp - 2) >> 2;         // 0 for warps 2..5, 1 for warps 6..9
-      const int t = m_tile * kGemmBM + quarter * 32 + lane;
-      const uint32_t lane_addr = tmem_acc + ((uint32_t)(quarter * 32) << 16);
-      uint32_t v[32];
-      if constexpr (EPI == 0) {
-#pragma unroll 1
-        for (int cb = 0; cb < 2; ++cb) {
-          int c0 = second * 64 + cb * 32;
-          tmem_ld32(lane_addr + c0, v);
-          int nbase = n_tile * kGemmBN + c0;
-          if (t < g.T) {
-            float* dst = g.outF + ((size_t)ks * g.T + t) * g.N + nbase;
-            const float* sc = g.wscale + nbase;
-#pragma unroll
-            for (int c = 0; c < 32; c += 4) {
-              if (nbase + c + 3 < g.N) {
-                float4 o = make_float4(__uint_as_float(v[c]) * sc[c], __uint_as_float(v[c + 1]) * sc[c + 1],
-                                       __uint_as_float(v[c + 2]) * sc[c + 2], __uint_as_float(v[c + 3]) * sc[c + 3]);
-                *reinterpret_cast<float4*>(dst + c) = o;
-              } else {
-                for (int e = 0; e < 4; ++e)
-                  if (nbase + c + e < g.N) dst[c + e] = __uint_as_float(v[c + e]) * sc[c + e];
-              }
-            }
-          }
-        }
-      } else {
-        // tile columns 0..63 are gate rows, 64..127 the matching up rows
-        uint32_t u[32];
-        int c0 = second * 32;
-        tmem_ld32(lane_addr + c0, v);
-        tmem_ld32(lane_addr + 64 + c0, u);
-        int fbase = n_tile * 64 + c0;            // index into the ffn dimension
-        const int F = g.N / 2;
-        if (t < g.T) {
-          const float* scg = g.wscale + n_tile * kGemmBN + c0;
-          const float* scu = scg + 64;
-          __nv_bfloat16* dst = g.outB + (size_t)t * F + fbase;
-#pragma unroll
-          for (int c = 0; c < 32; c += 2) {
-            float a0 = gelu_tanh(__uint_as_float(v[c]) * scg[c]) * (__uint_as_float(u[c]) * scu[c]);
-            float a1 = gelu_tanh(__uint_as_float(v[c + 1]) * scg[c + 1]) * (__uint_as_float(u[c + 1]) * scu[c + 1]);
-            if (fbase + c + 1 < F) {
-              *reinterpret_cast<__nv_bfloat162*>(dst + c) = __floats2bfloat162_rn(a0, a1);
-            } else if (fbase + c < F) {
-              dst[c] = __float2bfloat16(a0);
-            }
-          }
-        }
-      }
-    }
-  }
-  tc_fence_before();
-  __syncthreads();
-  if (*reinterpret_cast<volatile int*>(g.err) == (int)kDevBarrierTimeout) {
-    // a wait gave up: let any bulk copy still in flight land before the CTA retires
-    for (int i = 0; i < 2000; ++i) __nanosleep(100);
-    __syncthreads();
-  }
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_acc, kGemmBN);
-  }
-}
+#ifdef B2_GEMM_TRACE
+#define B2_GT(i) do { if (g.trace && gt_slot >= 0) g.trace[gt_slot * 512 + (i)] = clock64(); } while (0)
+#else
+#define B2_GT(i) do { } while (0)
+#endif
 
 }  // namespace b200lm
