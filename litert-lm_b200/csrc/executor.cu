@@ -511,13 +511,12 @@ void Executor::check_device_error(const char* where) {
 // x += rmsnorm(sum of split-K partials) * g_post ; h = bf16(rmsnorm(x) * g_pre)
 static void launch_resid_norm(cudaStream_t st, const float* parts, int nparts, int T, const ModelDims& d,
                               const float* g_post, const float* g_pre, float* xres, __nv_bfloat16* h) {
-  const int per_lane = (d.d / 4 + 31) / 32;
+  const int d4 = d.d / 4;
   const size_t stride = (size_t)T * d.d;
-  const int grid = (T + 7) / 8;
-  if (per_lane <= 4)
-    pf_resid_norm_warp_kernel<4><<<grid, 256, 0, st>>>(parts, nparts, stride, d.d, T, d.eps, g_post, g_pre, xres, h);
-  else if (per_lane <= 12)
-    pf_resid_norm_warp_kernel<12><<<grid, 256, 0, st>>>(parts, nparts, stride, d.d, T, d.eps, g_post, g_pre, xres, h);
+  if (d4 <= 128 * 3)
+    pf_resid_norm_reg_kernel<128, 3><<<T, 128, 0, st>>>(parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
+  else if (d4 <= 256 * 6)
+    pf_resid_norm_reg_kernel<256, 6><<<T, 256, 0, st>>>(parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
   else
     pf_resid_norm_kernel<<<T, kPfThreads, sizeof(float) * d.d, st>>>(parts, nparts, stride, d.d, d.eps, g_post, g_pre,
                                                                     xres, h);
@@ -527,10 +526,18 @@ template <typename T>
 static void launch_kv_append(cudaStream_t st, const ModelDims& d, int T_, const float* qkv, int nparts, int pos0, const int* pt,
                              const LayerWeights& L, const float* c, const float* s, const LayerKv& kv,
                              __nv_bfloat16* qout) {
-  const int threads = qout ? 256 : kPfThreads;      // more heads per token when queries are prepared too
-  const size_t smem = nparts > 1 ? sizeof(float) * d.nqkv() : 0;
-  pf_kv_append_kernel<T><<<T_, threads, smem, st>>>(d, qkv, nparts, (size_t)T_ * d.nqkv(), pos0, pt, L.g_k, c, s, kv,
-                                                    L.g_q, qout);
+  const int jobs = T_ * (d.hkv + (qout ? d.hq : 0));
+  const int per = kKvaThreads / 32;
+  const int grid = (jobs + per - 1) / per;
+  const size_t stride = (size_t)T_ * d.nqkv();
+#define B2_KVA(HD_) pf_kv_append_kernel<T, HD_><<<grid, kKvaThreads, 0, st>>>(d, qkv, nparts, stride, T_, pos0, pt, L.g_k, c, s, kv, L.g_q, qout)
+  switch (d.hd) {
+    case 32: B2_KVA(32); break;
+    case 64: B2_KVA(64); break;
+    case 128: B2_KVA(128); break;
+    default: B2_KVA(256); break;
+  }
+#undef B2_KVA
 }
 
 void Executor::run_prefill_chunk(const int* tokens, int T, int start) {

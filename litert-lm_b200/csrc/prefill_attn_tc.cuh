@@ -5,9 +5,12 @@
 // once for all heads that share it).  Keys are walked in tiles of 64:
 //
 //   S  = Q K^T        tcgen05.mma  M128 N64  K=hd   (Q, K tiles by TMA, K-major)
-//   P  = exp(S - B)   softmax warps: tcgen05.ld, mask, exp2, bf16 -> shared memory
-//   O += P V          tcgen05.mma  M128 N=hd K64    (V comes from a TRANSPOSED bf16
-//                                                    copy of the cache, so it is K-major too)
+//   P  = exp(S - B)   softmax warps: tcgen05.ld, mask, exp2, bf16, tcgen05.st back
+//                     into the columns S came from
+//   O += P V          tcgen05.mma  M128 N=hd K64    (P is the A operand in tensor
+//                                                    memory; V comes from a TRANSPOSED
+//                                                    bf16 copy of the cache, so it is
+//                                                    K-major in shared memory)
 //
 // Q and K are RMS-normalised per head before the product, so every score obeys
 // |s| <= B = sqrt(hd) max|g_q| max|g_k|.  The softmax is therefore shifted by the
@@ -15,18 +18,25 @@
 // overflow, and the O accumulator in tensor memory never has to be rescaled.
 // (Layers whose bound is too large for fp32 exponents use the CUDA-core kernel.)
 //
-// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (owns TMEM), warps 2-5
-// softmax + epilogue (one thread per query row = TMEM lane).  K/V tiles are
-// double buffered.  All waits are bounded.
+// S is double buffered in tensor memory and the MMA warp issues S(j+1) before
+// P(j) V(j), so the tensor pipe works on the next scores while the softmax
+// warps turn the current ones into probabilities.  K and V tiles have their
+// own two-stage rings: a K stage is released by the S product that read it, a
+// V stage by the P V product.
+//
+// Warp roles: warp 0 TMA producer, warp 1 MMA issuer (owns TMEM), warps 2-9
+// softmax + epilogue (two threads per query row = TMEM lane, 32 keys each).
+// All waits are bounded.
 #pragma once
 #include <cuda.h>
 
 #include "common.cuh"
 #include "prefill_ops.cuh"
+#include "prefill_gemm_ts.cuh"
 
 namespace b200lm {
 
-constexpr int kFaThreads = 192;
+constexpr int kFaThreads = 320;
 constexpr int kFaBN = 64;            // keys per tile
 constexpr float kFaMaxBound = 40.0f; // exp(-2 * 40) is still a normal fp32 number
 
@@ -35,8 +45,7 @@ struct FaSmem {
   static constexpr int kQ = 128 * HD * 2;            // 128 rows, HD/64 sub-tiles of 128 B rows
   static constexpr int kK = kFaBN * HD * 2;          // per stage
   static constexpr int kV = HD * kFaBN * 2;          // per stage: HD rows of 64 keys
-  static constexpr int kP = 128 * kFaBN * 2;
-  static constexpr int kTotal = kQ + 2 * kK + 2 * kV + kP + 256 + 1024;
+  static constexpr int kTotal = kQ + 2 * kK + 2 * kV + 1024 + 1024;
 };
 
 struct FaArgs {
@@ -46,6 +55,12 @@ struct FaArgs {
   float bound;             // B
   int* err;
 };
+
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int HD>
 __global__ void __launch_bounds__(kFaThreads, 1)
@@ -57,25 +72,26 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   unsigned char* sQ = sm;
   unsigned char* sK = sQ + L::kQ;
   unsigned char* sV = sK + 2 * L::kK;
-  unsigned char* sP = sV + 2 * L::kV;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(sP + L::kP);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sV + 2 * L::kV);
   uint64_t* q_full = bars;            // Q tile landed
-  uint64_t* kv_full = bars + 1;       // [2]
-  uint64_t* kv_empty = bars + 3;      // [2] both MMAs of the tile are done with the stage
-  uint64_t* s_full = bars + 5;        // S = Q K^T complete
-  uint64_t* s_free = bars + 6;        // softmax has read S
-  uint64_t* p_full = bars + 7;        // P written to shared memory
-  uint64_t* p_empty = bars + 8;       // P V has consumed P
-  uint64_t* o_full = bars + 9;        // all MMAs complete
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 10);
+  uint64_t* k_full = bars + 1;        // [2]
+  uint64_t* k_empty = bars + 3;       // [2] S = Q K^T of the tile is done with the stage
+  uint64_t* v_full = bars + 5;        // [2]
+  uint64_t* v_empty = bars + 7;       // [2] P V of the tile is done with the stage
+  uint64_t* s_full = bars + 9;        // [2] scores complete in S buffer
+  uint64_t* p_full = bars + 11;       // [2] probabilities written over the scores
+  uint64_t* o_full = bars + 13;       // all MMAs complete
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 14);
+  volatile int* sm_fail = reinterpret_cast<volatile int*>(bars + 15);   // a softmax thread's wait gave up
+  float* l_part = reinterpret_cast<float*>(bars + 16);     // [128] row sums of the upper 32 keys
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = g.hq / g.hkv;
   const int TT = 128 / G;                       // tokens per tile
   const int t0 = blockIdx.x * TT, kvh = blockIdx.y;
   constexpr int KB = HD / 64;                   // 64-column blocks of the head dimension
-  constexpr uint32_t kTmemCols = HD + kFaBN <= 256 ? 256 : 512;
-  constexpr uint32_t kSCol = 0, kOCol = kFaBN;
+  constexpr uint32_t kTmemCols = HD + 2 * kFaBN <= 256 ? 256 : 512;
+  constexpr uint32_t kOCol = 0, kSCol = HD;     // O, then two S buffers of 64 columns
 
   // key range of this query tile
   const int qpos_min = g.start + t0;
@@ -86,12 +102,16 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    for (int s = 0; s < 2; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-    mbar_init(s_full, 1);
-    mbar_init(s_free, 128);
-    mbar_init(p_full, 128);
-    mbar_init(p_empty, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
+      mbar_init(&s_full[s], 1);
+      mbar_init(&p_full[s], 8);
+    }
     mbar_init(o_full, 1);
+    *sm_fail = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
@@ -101,6 +121,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   const uint32_t tmem = *tmem_slot;
 
   if (warp == 0) {
+    // ---- producer
+    bool ok = true;
     if (lane == 0) {
       // Q tile: KB boxes of 64 columns x (G heads x TT tokens) rows
       mbar_arrive_expect_tx(q_full, L::kQ);
@@ -110,54 +132,75 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
             ::"r"(smem_u32(sQ + kb * 128 * 128)), "l"(&tmQ), "r"(kb * 64), "r"(kvh * G), "r"(t0), "r"(smem_u32(q_full))
             : "memory");
       }
-      for (int j = 0; j < ntiles; ++j) {
-        const int s = j & 1, n = j >> 1;
-        if (n > 0 && !mbar_wait(&kv_empty[s], (n - 1) & 1, g.err)) break;
-        const int key0 = (tile_lo + j) * kFaBN;
-        const int page = g.page_table[key0 / kPage], slot0 = key0 % kPage;
-        mbar_arrive_expect_tx(&kv_full[s], L::kK + L::kV);
+    }
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j & 1, n = j >> 1;
+      const int key0 = (tile_lo + j) * kFaBN;
+      const int page = g.page_table[key0 / kPage], slot0 = key0 % kPage;
+      if (n > 0) ok = mbar_wait(&k_empty[s], (n - 1) & 1, g.err);
+      if (ok && lane == 0) {
+        mbar_arrive_expect_tx(&k_full[s], L::kK);
         const int krow = (page * g.hkv + kvh) * kPage + slot0;
         for (int kb = 0; kb < KB; ++kb)
-          tma_load_2d(sK + s * L::kK + kb * kFaBN * 128, &tmK, kb * 64, krow, &kv_full[s]);
-        tma_load_2d(sV + s * L::kV, &tmVt, slot0, (page * g.hkv + kvh) * HD, &kv_full[s]);
+          tma_load_2d(sK + s * L::kK + kb * kFaBN * 128, &tmK, kb * 64, krow, &k_full[s]);
       }
+      if (ok && n > 0) ok = mbar_wait(&v_empty[s], (n - 1) & 1, g.err);
+      if (ok && lane == 0) {
+        mbar_arrive_expect_tx(&v_full[s], L::kV);
+        tma_load_2d(sV + s * L::kV, &tmVt, slot0, (page * g.hkv + kvh) * HD, &v_full[s]);
+      }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      const uint32_t idesc_s = umma_idesc_bf16(128, kFaBN);
-      const uint32_t idesc_o = umma_idesc_bf16(128, HD);
-      bool ok = mbar_wait(q_full, 0, g.err);
-      for (int j = 0; j < ntiles && ok; ++j) {
-        const int s = j & 1, n = j >> 1;
-        ok = mbar_wait(&kv_full[s], n & 1, g.err);
-        if (ok && j > 0) ok = mbar_wait(s_free, (j - 1) & 1, g.err);
+    // ---- MMA issue: S(0), then per tile S(j+1) before P(j) V(j)
+    const uint32_t idesc_s = umma_idesc_bf16(128, kFaBN);
+    const uint32_t idesc_o = umma_idesc_bf16(128, HD);
+    auto issue_s = [&](int j) {
+      const int s = j & 1;
+#pragma unroll
+      for (int kb = 0; kb < KB; ++kb) {
+        const uint64_t qd = umma_desc_sw128(smem_u32(sQ + kb * 128 * 128));
+        const uint64_t kd = umma_desc_sw128(smem_u32(sK + s * L::kK + kb * kFaBN * 128));
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          umma_bf16(tmem + kSCol + s * kFaBN, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
+      }
+      umma_commit(&s_full[s]);
+      umma_commit(&k_empty[s]);
+    };
+    bool ok = mbar_wait(q_full, 0, g.err) && mbar_wait(&k_full[0], 0, g.err);
+    if (ok) {
+      tc_fence_after();
+      if (lane == 0) issue_s(0);
+      __syncwarp();
+    }
+    for (int j = 0; j < ntiles && ok; ++j) {
+      const int s = j & 1, n = j >> 1;
+      if (j + 1 < ntiles) {
+        ok = mbar_wait(&k_full[(j + 1) & 1], ((j + 1) >> 1) & 1, g.err);
         if (!ok) break;
         tc_fence_after();
-#pragma unroll
-        for (int kb = 0; kb < KB; ++kb) {
-          const uint64_t qd = umma_desc_sw128(smem_u32(sQ + kb * 128 * 128));
-          const uint64_t kd = umma_desc_sw128(smem_u32(sK + s * L::kK + kb * kFaBN * 128));
-#pragma unroll
-          for (int k = 0; k < 4; ++k)
-            umma_bf16(tmem + kSCol, qd + (uint64_t)(k * 2), kd + (uint64_t)(k * 2), idesc_s, (kb | k) ? 1u : 0u);
-        }
-        umma_commit(s_full);
-        ok = mbar_wait(p_full, j & 1, g.err);
-        if (!ok) break;
-        tc_fence_after();
-        const uint64_t pd = umma_desc_sw128(smem_u32(sP));
+        if (lane == 0) issue_s(j + 1);
+        __syncwarp();
+      }
+      ok = mbar_wait(&v_full[s], n & 1, g.err) && mbar_wait(&p_full[s], n & 1, g.err);
+      if (!ok) break;
+      tc_fence_after();
+      if (lane == 0) {
         const uint64_t vd = umma_desc_sw128(smem_u32(sV + s * L::kV));
 #pragma unroll
-        for (int k = 0; k < kFaBN / 16; ++k)
-          umma_bf16(tmem + kOCol, pd + (uint64_t)(k * 2), vd + (uint64_t)(k * 2), idesc_o, (j | k) ? 1u : 0u);
-        umma_commit(&kv_empty[s]);
-        umma_commit(p_empty);
+        for (int k = 0; k < kFaBN / 16; ++k)      // P: 8 TMEM columns per 16 keys
+          umma_bf16_ts(tmem + kOCol, tmem + kSCol + s * kFaBN + k * 8, vd + (uint64_t)(k * 2), idesc_o, (j | k) ? 1u : 0u);
+        umma_commit(&v_empty[s]);
       }
-      umma_commit(o_full);
+      __syncwarp();
     }
+    if (ok && lane == 0) umma_commit(o_full);
+    __syncwarp();
   } else {
-    // ---- softmax warps: thread = one query row = one TMEM lane
+    // ---- softmax warps: two threads per query row (TMEM lane), 32 keys each
     const int quarter = warp & 3;
+    const int khalf = (warp - 2) >> 2;                 // which 32 keys of the tile
     const int r = quarter * 32 + lane;                 // row of the tile: token r / G, head r % G
     const int tok = t0 + r / G;
     const int qpos = g.start + tok;
@@ -166,54 +209,72 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
     const float shift = g.bound * log2e;
     float lsum = 0.f;
     bool ok = true;
-    for (int j = 0; j < ntiles && ok; ++j) {
-      ok = mbar_wait(s_full, j & 1, g.err);
-      if (!ok) break;
-      tc_fence_after();
-      uint32_t v0[32], v1[32];
-      tmem_ld32(lane_addr + kSCol, v0);
-      tmem_ld32(lane_addr + kSCol + 32, v1);
-      tc_fence_before();
-      mbar_arrive(s_free);                              // S may be overwritten by the next Q K^T
-      const int key0 = (tile_lo + j) * kFaBN;
-      uint32_t packed[32];
+    // The eight warps leave this loop together: a thread whose wait gave up raises
+    // sm_fail before the named barrier, everyone reads it after.
+    for (int j = 0; j < ntiles; ++j) {
+      const int s = j & 1, n = j >> 1;
+      uint32_t packed[16];
+      if (!mbar_wait(&s_full[s], n & 1, g.err)) {
+        *sm_fail = 1;
+      } else {
+        tc_fence_after();
+        uint32_t v[32];
+        tmem_ld32(lane_addr + kSCol + s * kFaBN + khalf * 32, v);
+        const int key0 = (tile_lo + j) * kFaBN + khalf * 32;
+        // every row of the tile sees every key of an interior tile: no mask needed there
+        const bool interior = key0 + 31 <= qpos_min && (g.is_global || qpos_max - key0 < g.window);
+        if (interior) {
 #pragma unroll
-      for (int c = 0; c < 64; c += 2) {
-        float p[2];
+          for (int c = 0; c < 32; c += 2) {
+            const float p0 = ex2_approx(fmaf(__uint_as_float(v[c]), log2e, -shift));
+            const float p1 = ex2_approx(fmaf(__uint_as_float(v[c + 1]), log2e, -shift));
+            lsum += p0 + p1;
+            __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
+            packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
+        } else {
 #pragma unroll
-        for (int e = 0; e < 2; ++e) {
-          const int kpos = key0 + c + e;
-          const float sv = __uint_as_float(c + e < 32 ? v0[(c + e) & 31] : v1[(c + e) & 31]);
-          const bool open = kpos <= qpos && (g.is_global || qpos - kpos < g.window);
-          p[e] = open ? exp2f(sv * log2e - shift) : 0.f;
+          for (int c = 0; c < 32; c += 2) {
+            float p[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int kpos = key0 + c + e;
+              const bool open = kpos <= qpos && (g.is_global || qpos - kpos < g.window);
+              p[e] = open ? ex2_approx(fmaf(__uint_as_float(v[c + e]), log2e, -shift)) : 0.f;
+            }
+            lsum += p[0] + p[1];
+            __nv_bfloat162 h = __floats2bfloat162_rn(p[0], p[1]);
+            packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
+          }
         }
-        __nv_bfloat162 h = __floats2bfloat162_rn(p[0], p[1]);
-        // sum what the tensor core will actually multiply (the rounded values)
-        lsum += __low2float(h) + __high2float(h);
-        packed[c >> 1] = *reinterpret_cast<uint32_t*>(&h);
       }
-      if (j > 0) ok = mbar_wait(p_empty, (j - 1) & 1, g.err);   // P V of the previous tile has read P
-      if (!ok) break;
-      unsigned char* prow = sP + r * 128;
-#pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        const int chunk = c ^ (r & 7);
-        *reinterpret_cast<uint4*>(prow + chunk * 16) =
-            make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-      }
-      fence_async_smem();
-      mbar_arrive(p_full);
+      // The 16 columns a thread writes lie inside the 32 that it or the other thread
+      // of its row has just read, so all eight warps meet before anyone overwrites.
+      asm volatile("bar.sync 1, 256;" ::: "memory");
+      if (*sm_fail) { ok = false; break; }
+      tmem_st16(lane_addr + kSCol + s * kFaBN + khalf * 16, packed);
+      tmem_st_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full[s]);
     }
-    // ---- epilogue: O / l -> bf16
+    // ---- epilogue: O / l -> bf16; this thread writes half of the head dimension
+    if (khalf == 1) l_part[r] = lsum;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (khalf == 0) lsum += l_part[r];
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    if (khalf == 0) l_part[r] = lsum;
+    asm volatile("bar.sync 1, 256;" ::: "memory");
+    lsum = l_part[r];
     if (ok && mbar_wait(o_full, 0, g.err)) {
       tc_fence_after();
       const float inv = lsum > 0.f ? 1.0f / lsum : 0.f;
       const int head = kvh * G + (r % G);
-      __nv_bfloat16* dst = g.out + ((size_t)tok * g.hq + head) * HD;
+      __nv_bfloat16* dst = g.out + ((size_t)tok * g.hq + head) * HD + khalf * (HD / 2);
 #pragma unroll 1
-      for (int cb = 0; cb < HD / 32; ++cb) {
+      for (int cb = 0; cb < HD / 64; ++cb) {
         uint32_t o[32];
-        tmem_ld32(lane_addr + kOCol + cb * 32, o);
+        tmem_ld32(lane_addr + kOCol + khalf * (HD / 2) + cb * 32, o);
         if (tok < g.T) {
 #pragma unroll
           for (int c = 0; c < 32; c += 8) {

@@ -95,60 +95,73 @@ pf_resid_norm_kernel(const float* __restrict__ parts, int nparts, size_t part_st
     h[(size_t)t * d + i] = __float2bfloat16(pf_sm[i] * r2 * g_pre[i]);
 }
 
-// Same as pf_resid_norm_kernel, one WARP per token: the token's row lives in
-// registers (MAXV float4 per lane), sums are warp shuffles, every load is a
-// 16-byte load and the loads of one partial are independent.
-template <int MAXV>
-__global__ void __launch_bounds__(256)
-pf_resid_norm_warp_kernel(const float* __restrict__ parts, int nparts, size_t part_stride, int d, int T, float eps,
-                          const float* __restrict__ g_post, const float* __restrict__ g_pre,
-                          float* __restrict__ xres, __nv_bfloat16* __restrict__ h) {
-  const int lane = threadIdx.x & 31;
-  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (t >= T) return;
+// Same as pf_resid_norm_kernel with the token's row in registers: one CTA of
+// THREADS threads per token, MAXV float4 per thread, 16-byte loads, two block
+// reductions.  Small CTAs keep many tokens in flight per SM, which is what
+// hides the latency of the partial-sum loads.
+template <int THREADS, int MAXV>
+__global__ void __launch_bounds__(THREADS)
+pf_resid_norm_reg_kernel(const float* __restrict__ parts, int nparts, size_t part_stride, int d, float eps,
+                         const float* __restrict__ g_post, const float* __restrict__ g_pre,
+                         float* __restrict__ xres, __nv_bfloat16* __restrict__ h) {
+  __shared__ float red[2][THREADS / 32];
+  const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int d4 = d / 4;
-  float4 f[MAXV];
-  float ss = 0.f;
+  float4 f[MAXV], x[MAXV];
+  float4* xr = reinterpret_cast<float4*>(xres + (size_t)t * d);
 #pragma unroll
-  for (int u = 0; u < MAXV; ++u) f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int u = 0; u < MAXV; ++u) {
+    const int i = threadIdx.x + THREADS * u;
+    f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+    x[u] = i < d4 ? xr[i] : f[u];
+  }
   for (int p = 0; p < nparts; ++p) {
     const float4* src = reinterpret_cast<const float4*>(parts + (size_t)p * part_stride + (size_t)t * d);
 #pragma unroll
     for (int u = 0; u < MAXV; ++u) {
-      const int i = lane + 32 * u;
+      const int i = threadIdx.x + THREADS * u;
       if (i < d4) {
         float4 v = src[i];
         f[u].x += v.x; f[u].y += v.y; f[u].z += v.z; f[u].w += v.w;
       }
     }
   }
+  float ss = 0.f;
 #pragma unroll
   for (int u = 0; u < MAXV; ++u) ss += f[u].x * f[u].x + f[u].y * f[u].y + f[u].z * f[u].z + f[u].w * f[u].w;
   ss = warp_sum(ss);
+  if (lane == 0) red[0][warp] = ss;
+  __syncthreads();
+  ss = 0.f;
+#pragma unroll
+  for (int w = 0; w < THREADS / 32; ++w) ss += red[0][w];
   const float r = rsqrtf(ss / (float)d + eps);
-  float4* xr = reinterpret_cast<float4*>(xres + (size_t)t * d);
   float ss2 = 0.f;
 #pragma unroll
   for (int u = 0; u < MAXV; ++u) {
-    const int i = lane + 32 * u;
+    const int i = threadIdx.x + THREADS * u;
     if (i < d4) {
-      float4 x = xr[i], gp = reinterpret_cast<const float4*>(g_post)[i];
-      x.x += f[u].x * r * gp.x; x.y += f[u].y * r * gp.y; x.z += f[u].z * r * gp.z; x.w += f[u].w * r * gp.w;
-      xr[i] = x;
-      f[u] = x;
-      ss2 += x.x * x.x + x.y * x.y + x.z * x.z + x.w * x.w;
+      float4 gp = reinterpret_cast<const float4*>(g_post)[i];
+      x[u].x += f[u].x * r * gp.x; x[u].y += f[u].y * r * gp.y; x[u].z += f[u].z * r * gp.z; x[u].w += f[u].w * r * gp.w;
+      xr[i] = x[u];
+      ss2 += x[u].x * x[u].x + x[u].y * x[u].y + x[u].z * x[u].z + x[u].w * x[u].w;
     }
   }
   if (g_pre == nullptr) return;
   ss2 = warp_sum(ss2);
+  if (lane == 0) red[1][warp] = ss2;
+  __syncthreads();
+  ss2 = 0.f;
+#pragma unroll
+  for (int w = 0; w < THREADS / 32; ++w) ss2 += red[1][w];
   const float r2 = rsqrtf(ss2 / (float)d + eps);
 #pragma unroll
   for (int u = 0; u < MAXV; ++u) {
-    const int i = lane + 32 * u;
+    const int i = threadIdx.x + THREADS * u;
     if (i < d4) {
       float4 gq = reinterpret_cast<const float4*>(g_pre)[i];
-      __nv_bfloat162 a = __floats2bfloat162_rn(f[u].x * r2 * gq.x, f[u].y * r2 * gq.y);
-      __nv_bfloat162 b = __floats2bfloat162_rn(f[u].z * r2 * gq.z, f[u].w * r2 * gq.w);
+      __nv_bfloat162 a = __floats2bfloat162_rn(x[u].x * r2 * gq.x, x[u].y * r2 * gq.y);
+      __nv_bfloat162 b = __floats2bfloat162_rn(x[u].z * r2 * gq.z, x[u].w * r2 * gq.w);
       uint2 w;
       w.x = *reinterpret_cast<uint32_t*>(&a);
       w.y = *reinterpret_cast<uint32_t*>(&b);
@@ -157,83 +170,128 @@ pf_resid_norm_warp_kernel(const float* __restrict__ parts, int nparts, size_t pa
   }
 }
 
+// V consecutive floats (V = 1, 2 or 4) with one load / store; p is V*4-byte aligned
+template <int V>
+__device__ __forceinline__ void ld_vec(const float* p, float (&o)[V]) {
+  if constexpr (V == 4) { float4 v = *reinterpret_cast<const float4*>(p); o[0] = v.x; o[1] = v.y; o[2] = v.z; o[3] = v.w; }
+  else if constexpr (V == 2) { float2 v = *reinterpret_cast<const float2*>(p); o[0] = v.x; o[1] = v.y; }
+  else o[0] = *p;
+}
+template <int V>
+__device__ __forceinline__ void st_vec(float* p, const float (&o)[V]) {
+  if constexpr (V == 4) *reinterpret_cast<float4*>(p) = make_float4(o[0], o[1], o[2], o[3]);
+  else if constexpr (V == 2) *reinterpret_cast<float2*>(p) = make_float2(o[0], o[1]);
+  else *p = o[0];
+}
+template <int V>
+__device__ __forceinline__ void st_vec(__nv_bfloat16* p, const float (&o)[V]) {
+  if constexpr (V == 4) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(o[0], o[1]), b = __floats2bfloat162_rn(o[2], o[3]);
+    uint2 w;
+    w.x = *reinterpret_cast<uint32_t*>(&a);
+    w.y = *reinterpret_cast<uint32_t*>(&b);
+    *reinterpret_cast<uint2*>(p) = w;
+  } else if constexpr (V == 2) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(o[0], o[1]);
+  } else {
+    *p = __float2bfloat16(o[0]);
+  }
+}
+
 // K-RMSNorm + RoPE on the new keys, then K and V rows into the paged cache (and
 // the bf16 operands of the tensor-core attention); with qout, also Q-RMSNorm +
-// RoPE + 1/sqrt(hd) on the query heads into a bf16 [T][hq][hd] buffer.  One CTA
-// per token; one warp per head (looped).  The QKV row may arrive as `nparts`
-// split-K partial sums `part_stride` floats apart; they are added into shared
-// memory (nqkv floats of dynamic shared memory) first.
-template <typename T>
-__global__ void __launch_bounds__(256)
-pf_kv_append_kernel(ModelDims dm, const float* __restrict__ qkv, int nparts, size_t part_stride, int pos0,
+// RoPE + 1/sqrt(hd) on the query heads into a bf16 [T][hq][hd] buffer.  One
+// warp per (token, head): job = token * nheads + head, kv heads first.  Lane l
+// holds V consecutive elements of each half of the head (V = HD / 64, or one
+// element on the low lanes for HD 32).  The QKV row may arrive as `nparts`
+// split-K partial sums `part_stride` floats apart; they are added on load.
+constexpr int kKvaThreads = 128;
+template <typename T, int HD>
+__global__ void __launch_bounds__(kKvaThreads, HD == 256 ? 8 : 10)
+pf_kv_append_kernel(ModelDims dm, const float* __restrict__ qkv, int nparts, size_t part_stride, int ntok, int pos0,
                     const int* __restrict__ page_table, const float* __restrict__ g_k,
                     const float* __restrict__ cosT, const float* __restrict__ sinT, LayerKv kv,
                     const float* __restrict__ g_q, __nv_bfloat16* __restrict__ qout) {
-  const int t = blockIdx.x, pos = pos0 + t;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
-  const int hd = dm.hd, half = hd / 2;
-  extern __shared__ __align__(16) float kv_row[];
-  const float* row = qkv + (size_t)t * dm.nqkv();
-  if (nparts > 1) {
-    const int n4 = dm.nqkv() / 4;
-    for (int i = threadIdx.x; i < n4; i += blockDim.x) {
-      float4 a = reinterpret_cast<const float4*>(row)[i];
-      for (int p = 1; p < nparts; ++p) {
-        float4 b = reinterpret_cast<const float4*>(row + p * part_stride)[i];
-        a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+  constexpr int V = HD >= 64 ? HD / 64 : 1;
+  constexpr int half = HD / 2;
+  const int lane = threadIdx.x & 31;
+  const int nheads = dm.hkv + (qout ? dm.hq : 0);
+  const int job = blockIdx.x * (kKvaThreads / 32) + (threadIdx.x >> 5);
+  if (job >= ntok * nheads) return;
+  const int t = job / nheads, h = job - t * nheads, pos = pos0 + t;
+  const bool is_q = h >= dm.hkv;
+  const int e0 = lane * V;
+  const bool act = e0 < half;                                   // HD 32: lanes 16..31 idle
+  // head offset within the QKV row: [q heads | k heads | v heads]
+  const int col = is_q ? (h - dm.hkv) * HD : dm.nq() + h * HD;
+  const float* row = qkv + (size_t)t * dm.nqkv() + col;
+  float a[V], b[V], va[V], vb[V];
+#pragma unroll
+  for (int i = 0; i < V; ++i) a[i] = b[i] = va[i] = vb[i] = 0.f;
+  if (act) {
+    for (int p = 0; p < nparts; ++p) {
+      const float* src = row + (size_t)p * part_stride;
+      float x[V], y[V];
+      ld_vec<V>(src + e0, x);
+      ld_vec<V>(src + e0 + half, y);
+#pragma unroll
+      for (int i = 0; i < V; ++i) { a[i] += x[i]; b[i] += y[i]; }
+      if (!is_q) {
+        ld_vec<V>(src + dm.nkv() + e0, x);
+        ld_vec<V>(src + dm.nkv() + e0 + half, y);
+#pragma unroll
+        for (int i = 0; i < V; ++i) { va[i] += x[i]; vb[i] += y[i]; }
       }
-      reinterpret_cast<float4*>(kv_row)[i] = a;
     }
-    __syncthreads();
-    row = kv_row;
+  }
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < V; ++i) ss += a[i] * a[i] + b[i] * b[i];
+  ss = warp_sum(ss);
+  float r = rsqrtf(ss / (float)HD + dm.eps);
+  if (is_q) r *= rsqrtf((float)HD);
+  if (!act) return;
+  const float* gain = is_q ? g_q : g_k;
+  float k0[V], k1[V];
+  {
+    float ga[V], gb[V], cs[V], sn[V];
+    ld_vec<V>(gain + e0, ga);
+    ld_vec<V>(gain + e0 + half, gb);
+    ld_vec<V>(cosT + (size_t)pos * half + e0, cs);
+    ld_vec<V>(sinT + (size_t)pos * half + e0, sn);
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const float a0 = a[i] * r * ga[i], b0 = b[i] * r * gb[i];
+      k0[i] = a0 * cs[i] - b0 * sn[i];
+      k1[i] = b0 * cs[i] + a0 * sn[i];
+    }
+  }
+  if (is_q) {
+    __nv_bfloat16* dst = qout + ((size_t)t * dm.hq + (h - dm.hkv)) * HD;
+    st_vec<V>(dst + e0, k0);
+    st_vec<V>(dst + e0 + half, k1);
+    return;
   }
   const int page = page_table[pos / kPage], slot = pos % kPage;
+  const size_t off = (((size_t)page * dm.hkv + h) * kPage + slot) * HD;
   T* kbase = reinterpret_cast<T*>(kv.k);
   T* vbase = reinterpret_cast<T*>(kv.v);
-  const int nheads = dm.hkv + (qout ? dm.hq : 0);
-  for (int h = warp; h < nheads; h += nwarps) {
-    if (h >= dm.hkv) {           // a query head
-      const int qh = h - dm.hkv;
-      const float* qs = row + (size_t)qh * hd;
-      float ss = 0.f;
-      for (int e = lane; e < hd; e += 32) ss += qs[e] * qs[e];
-      ss = warp_sum(ss);
-      const float r = rsqrtf(ss / (float)hd + dm.eps) * rsqrtf((float)hd);
-      __nv_bfloat16* dst = qout + ((size_t)t * dm.hq + qh) * hd;
-      for (int e = lane; e < half; e += 32) {
-        float a0 = qs[e] * r * g_q[e], b0 = qs[e + half] * r * g_q[e + half];
-        float cs = cosT[(size_t)pos * half + e], sn = sinT[(size_t)pos * half + e];
-        dst[e] = __float2bfloat16(a0 * cs - b0 * sn);
-        dst[e + half] = __float2bfloat16(b0 * cs + a0 * sn);
-      }
-      continue;
+  st_vec<V>(kbase + off + e0, k0);
+  st_vec<V>(kbase + off + e0 + half, k1);
+  st_vec<V>(vbase + off + e0, va);
+  st_vec<V>(vbase + off + e0 + half, vb);
+  if constexpr (sizeof(T) == 4) {
+    if (kv.k16) {
+      st_vec<V>(kv.k16 + off + e0, k0);
+      st_vec<V>(kv.k16 + off + e0 + half, k1);
     }
-    const int kh = h;
-    const float* ks = row + dm.nq() + (size_t)kh * hd;
-    const float* vs = row + dm.nq() + dm.nkv() + (size_t)kh * hd;
-    size_t off = (((size_t)page * dm.hkv + kh) * kPage + slot) * hd;
-    float ss = 0.f;
-    for (int e = lane; e < hd; e += 32) ss += ks[e] * ks[e];
-    ss = warp_sum(ss);
-    float r = rsqrtf(ss / (float)hd + dm.eps);
-    for (int e = lane; e < half; e += 32) {
-      float a0 = ks[e] * r * g_k[e], b0 = ks[e + half] * r * g_k[e + half];
-      float cs = cosT[(size_t)pos * half + e], sn = sinT[(size_t)pos * half + e];
-      float k0 = a0 * cs - b0 * sn, k1 = b0 * cs + a0 * sn;
-      float v0 = vs[e], v1 = vs[e + half];
-      if constexpr (sizeof(T) == 4) {
-        kbase[off + e] = k0; kbase[off + e + half] = k1;
-        vbase[off + e] = v0; vbase[off + e + half] = v1;
-        if (kv.k16) { kv.k16[off + e] = __float2bfloat16(k0); kv.k16[off + e + half] = __float2bfloat16(k1); }
-      } else {
-        kbase[off + e] = __float2bfloat16(k0); kbase[off + e + half] = __float2bfloat16(k1);
-        vbase[off + e] = __float2bfloat16(v0); vbase[off + e + half] = __float2bfloat16(v1);
-      }
-      if (kv.v16) {
-        size_t vt = (((size_t)page * dm.hkv + kh) * hd + e) * kPage + slot;
-        kv.v16[vt] = __float2bfloat16(v0);
-        kv.v16[vt + (size_t)half * kPage] = __float2bfloat16(v1);
-      }
+  }
+  if (kv.v16) {
+#pragma unroll
+    for (int i = 0; i < V; ++i) {
+      const size_t vt = (((size_t)page * dm.hkv + h) * HD + e0 + i) * kPage + slot;
+      kv.v16[vt] = __float2bfloat16(va[i]);
+      kv.v16[vt + (size_t)half * kPage] = __float2bfloat16(vb[i]);
     }
   }
 }
