@@ -32,6 +32,8 @@ import __graft_entry__ as graft  # noqa: E402
 
 PREFILL_TOKENS = 1024
 DECODE_STEPS = 256
+# DRAM bytes per decode step in the ncu capture under profiles/ (a launch of two steps read 1082.8 MB and wrote 28.1 MB)
+DECODE_DRAM_BYTES_PER_STEP = 555.5e6
 METRIC = "decode tok/s (256 greedy steps after a 1024-token prefill), Gemma3-1B-shaped int4, batch 1 per GPU"
 
 
@@ -150,9 +152,21 @@ def host_threads() -> int:
         return os.cpu_count() or 1
 
 
+def use_all_host_threads() -> None:
+    """torchrun exports OMP_NUM_THREADS=1 to its children; the CPU arm wants every core it may
+    run on.  Must be called before the oracle library (OpenMP) is loaded."""
+    if "TORCHELASTIC_RUN_ID" in os.environ or "B200LM_CPU_THREADS" in os.environ:
+        try:
+            n = len(os.sched_getaffinity(0))
+        except Exception:
+            n = os.cpu_count() or 1
+        os.environ["OMP_NUM_THREADS"] = os.environ.get("B200LM_CPU_THREADS", str(n))
+
+
 def run_reference(args, rank: int) -> None:
     if rank != 0:
         return
+    use_all_host_threads()
     cfg, rec, _ = load_model(args.model)
     pt, ds = 32, 8
     sample = (f"CPU oracle port (plain C, OpenMP): prefill of {pt} seeded ids then {ds} greedy decode steps at that "
@@ -216,13 +230,23 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     graft.build()
     pkg = graft.load_package()
-    cfg, rec, img = load_model(args.model)
+    if world > 1:
+        # rank 0 generates (or finds) the cached model file; the others read it afterwards
+        if rank == 0:
+            cfg, rec, img = load_model(args.model)
+        dist.barrier()
+        if rank != 0:
+            cfg, rec, img = load_model(args.model)
+    else:
+        cfg, rec, img = load_model(args.model)
     stream = torch.cuda.Stream()          # a real (non-default) stream: CUDA events below are recorded on it
     torch.cuda.set_stream(stream)
     ex = pkg.B200LlmExecutor(img, device=local_rank, decode_mode=args.decode_mode, prefill_gemm=args.prefill_gemm,
                              stream=stream.cuda_stream)
-    # every rank runs its own session on its own seeded prompt
-    ids = np.random.Generator(np.random.PCG64(cfg.seed + 1000 * rank)).integers(0, cfg.vocab, PREFILL_TOKENS).astype(np.int32)
+    # one session per GPU; session ids are sharded over the ranks, each with its own seeded prompt
+    session = pkg.sharding.shard_sessions(world, world, rank)[0]
+    ids = np.random.Generator(np.random.PCG64(pkg.sharding.session_seed(cfg.seed, session))).integers(
+        0, cfg.vocab, PREFILL_TOKENS).astype(np.int32)
 
     def barrier():
         torch.cuda.synchronize()
@@ -273,11 +297,9 @@ def main() -> None:
     barrier()
     clocks = sampler.finish()
     launches = ex.GetLaunchCount() - launches0
-    t = torch.tensor([sum(pf_ms), sum(dec_ms)], dtype=torch.float64, device="cuda")
-    if world > 1:
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    pf_total, dec_total = float(t[0]), float(t[1])
-    decode_tok_s = world * args.steps * DECODE_STEPS / (dec_total / 1e3)
+    # whole job: tokens summed over ranks, device times (CUDA events) maxed over ranks
+    dec_tokens, (pf_total, dec_total) = pkg.sharding.reduce_throughput(args.steps * DECODE_STEPS, [sum(pf_ms), sum(dec_ms)])
+    decode_tok_s = dec_tokens / (dec_total / 1e3)
     prefill_tok_s = world * args.steps * PREFILL_TOKENS / (pf_total / 1e3)
 
     e2e = None
@@ -331,11 +353,13 @@ def main() -> None:
         "e2e": e2e,
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                     "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": None, "of": peaks["source"],
+                     "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": DECODE_DRAM_BYTES_PER_STEP, "of": peaks["source"],
+                     "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one decode-step launch, from the "
+                                     "ncu capture summarised in profiles/decode_stream_kernel_gemma3-1b.md",
                      "kernel": "decode step (all phases)", "algorithmic_bytes_per_token": bytes_per_tok,
                      "frac_of_nominal_8TBs": achieved_gbs / 8000.0},
     }
-    if not args.no_cpu_baseline and world >= 1:
+    if not args.no_cpu_baseline and world == 1:
         pt, ds = 32, 8
         t0 = time.perf_counter()
         p, d = cpu_sample(rec, cfg, pt, ds)
