@@ -60,6 +60,18 @@ int B200LmOps_Attention(int32_t device, const float* q, const float* k, const fl
                         int32_t kv_bf16, int32_t nsplit, int32_t repeat, float* out, float* ms_out,
                         char** err);
 
+/* Causal self-attention over s tokens on the tensor cores (the prefill flash
+ * kernel of the executor: TMA-staged K/V tiles, tcgen05 MMA with TMEM
+ * accumulators, GQA-packed query tiles).  q [s][hq][hd], k, v [s][hkv][hd] fp32
+ * host, rounded to bf16 on the device; scores are q.k / sqrt(hd); window <= 0
+ * means global.  hd must be 128 or 256.  The kernel shifts the softmax by a
+ * constant bound on the scores instead of a running maximum; inputs whose
+ * scores could exceed 40 are rejected with FailedPrecondition.  repeat > 1
+ * re-runs the kernel and returns the mean device time in ms_out. */
+int B200LmOps_AttentionPrefillTc(int32_t device, const float* q, const float* k, const float* v, int32_t s,
+                                 int32_t hq, int32_t hkv, int32_t hd, int32_t window, int32_t repeat, float* out,
+                                 float* ms_out, char** err);
+
 /* Split-KV decode attention that allocates nothing.  It has no counterpart in
  * the reference.  It is for callers that may not allocate device memory when
  * they call in: code running inside another runtime's execution callback, a

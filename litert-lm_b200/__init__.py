@@ -57,7 +57,8 @@ _EXEC_SYMBOLS = ["B200Lm_Create", "B200Lm_CreateShared", "B200Lm_Destroy", "B200
                  "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_BackendName", "B200Lm_Synchronize",
                  "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount", "B200Lm_TraceDecodeStep"]
 _OPS_SYMBOLS = ["B200LmOps_RepackW4T", "B200LmOps_RepackW4G", "B200LmOps_UnpackW4", "B200LmOps_GemvW4",
-                "B200LmOps_GemmW4", "B200LmOps_GemmGegluW4", "B200LmOps_Attention", "B200LmOps_AttentionDecodeStatic"]
+                "B200LmOps_GemmW4", "B200LmOps_GemmGegluW4", "B200LmOps_Attention", "B200LmOps_AttentionPrefillTc",
+                "B200LmOps_AttentionDecodeStatic"]
 
 
 def load_library() -> C.CDLL:
@@ -94,6 +95,7 @@ def load_library() -> C.CDLL:
         "B200LmOps_GemmW4": [i32, i32, vp, vp, i64, i64, vp, i32, i32, i32, vp, vp, errp],
         "B200LmOps_GemmGegluW4": [i32, i32, vp, vp, vp, vp, i64, i64, vp, i32, vp, errp],
         "B200LmOps_Attention": [i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, errp],
+        "B200LmOps_AttentionPrefillTc": [i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, errp],
         "B200LmOps_AttentionDecodeStatic": [i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, errp],
     }
     for name, args in sig.items():
@@ -331,6 +333,21 @@ class ops:
         ms = C.c_float(0)
         _call("B200LmOps_Attention", device, _ptr(q), _ptr(k), _ptr(v), t, s, hq, hkv, hd, qpos0, window, int(kv_bf16),
               nsplit, repeat, _ptr(out), C.byref(ms))
+        return out, ms.value
+
+    @staticmethod
+    def attention_prefill_tc(q: np.ndarray, k: np.ndarray, v: np.ndarray, window: int = 0, repeat: int = 1,
+                             device: int = 0) -> Tuple[np.ndarray, float]:
+        """Causal self-attention of s tokens with the tensor-core prefill kernel (bf16 operands)."""
+        q = np.ascontiguousarray(q, dtype=np.float32)
+        k = np.ascontiguousarray(k, dtype=np.float32)
+        v = np.ascontiguousarray(v, dtype=np.float32)
+        s, hq, hd = q.shape
+        _, hkv, _ = k.shape
+        out = np.empty_like(q)
+        ms = C.c_float(0)
+        _call("B200LmOps_AttentionPrefillTc", device, _ptr(q), _ptr(k), _ptr(v), s, hq, hkv, hd, window, repeat,
+              _ptr(out), C.byref(ms))
         return out, ms.value
 
     @staticmethod

@@ -80,6 +80,15 @@ __device__ __forceinline__ float gelu_tanh(float x) {
   const float c = 0.7978845608028654f;
   return 0.5f * x * (1.0f + tanhf(c * (x + 0.044715f * x * x * x)));
 }
+// Programmatic dependent launch.  A kernel launched with programmatic stream
+// serialisation may start while its predecessor in the stream still runs;
+// pdl_wait() blocks until the predecessor has completed and its writes are
+// visible (a no-op for an ordinary launch).  Nothing before it may touch memory
+// the predecessor reads or writes.  pdl_launch_dependents() lets the successor
+// start its own set-up once every CTA of this grid has got here.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ uint4 ldg_nc_v4(const uint4* p) {
   uint4 v;
   asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"

@@ -238,6 +238,25 @@ static CUtensorMap make_bf16_map(const void* base, int rank, const cuuint64_t* d
   return tm;
 }
 
+// Launch with programmatic stream serialisation: the kernel may be scheduled
+// while its predecessor in the stream is still running and does its set-up
+// (barrier init, TMEM allocation) there; it calls pdl_wait() before it touches
+// the predecessor's data.
+template <typename... KArgs, typename... Args>
+static void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at;
+  cfg.numAttrs = 1;
+  B2_CUDA(cudaLaunchKernelEx(&cfg, kernel, KArgs(std::forward<Args>(args))...));
+}
+
 // Split-K factor for a GEMM of `n_tiles` weight-row tiles over T tokens with KB
 // 64-wide k blocks: the smallest divisor of KB (at least 4 k blocks per split,
 // at most 8 splits) whose work units fill 90 % of the last round over the SMs,
@@ -275,8 +294,8 @@ void launch_gemm(cudaStream_t st, int mode, const CUtensorMap& a_map, const __nv
     const int sms = sms_of[dev];
     const int total = ((N + kTsRows - 1) / kTsRows) * ((T + kTsTok - 1) / kTsTok) * ksplit;
     const int grid = total < sms ? total : sms;
-    if (geglu) gemm_w4_ts_kernel<1><<<grid, kTsThreads, kTsSmem, st>>>(a_map, g);
-    else gemm_w4_ts_kernel<0><<<grid, kTsThreads, kTsSmem, st>>>(a_map, g);
+    if (geglu) launch_pdl(gemm_w4_ts_kernel<1>, dim3(grid), dim3(kTsThreads), kTsSmem, st, a_map, g);
+    else launch_pdl(gemm_w4_ts_kernel<0>, dim3(grid), dim3(kTsThreads), kTsSmem, st, a_map, g);
   } else {
     B2_CHECK(ksplit == 1, kInternal, "the check GEMM does not split K");
     dim3 grid(geglu ? N / 32 : N / 16, (T + 7) / 8);
@@ -514,9 +533,9 @@ static void launch_resid_norm(cudaStream_t st, const float* parts, int nparts, i
   const int d4 = d.d / 4;
   const size_t stride = (size_t)T * d.d;
   if (d4 <= 128 * 3)
-    pf_resid_norm_reg_kernel<128, 3><<<T, 128, 0, st>>>(parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
+    launch_pdl(pf_resid_norm_reg_kernel<128, 3>, dim3(T), dim3(128), 0, st, parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
   else if (d4 <= 256 * 6)
-    pf_resid_norm_reg_kernel<256, 6><<<T, 256, 0, st>>>(parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
+    launch_pdl(pf_resid_norm_reg_kernel<256, 6>, dim3(T), dim3(256), 0, st, parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
   else
     pf_resid_norm_kernel<<<T, kPfThreads, sizeof(float) * d.d, st>>>(parts, nparts, stride, d.d, d.eps, g_post, g_pre,
                                                                     xres, h);
@@ -530,7 +549,7 @@ static void launch_kv_append(cudaStream_t st, const ModelDims& d, int T_, const 
   const int per = kKvaThreads / 32;
   const int grid = (jobs + per - 1) / per;
   const size_t stride = (size_t)T_ * d.nqkv();
-#define B2_KVA(HD_) pf_kv_append_kernel<T, HD_><<<grid, kKvaThreads, 0, st>>>(d, qkv, nparts, stride, T_, pos0, pt, L.g_k, c, s, kv, L.g_q, qout)
+#define B2_KVA(HD_) launch_pdl(pf_kv_append_kernel<T, HD_>, dim3(grid), dim3(kKvaThreads), 0, st, d, qkv, nparts, stride, T_, pos0, pt, L.g_k, c, s, kv, L.g_q, qout)
   switch (d.hd) {
     case 32: B2_KVA(32); break;
     case 64: B2_KVA(64); break;
@@ -581,8 +600,8 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
       FaArgs fa{T, start, d.hq, d.hkv, d.window, L.is_global, page_table_dev, pf_attn, model->attn_bound[li], err};
       const int TT = 128 / d.group();
       dim3 grid((T + TT - 1) / TT, d.hkv);
-      if (d.hd == 256) flash_prefill_tc_kernel<256><<<grid, kFaThreads, FaSmem<256>::kTotal, stream>>>(tm_q, tm_k[li], tm_vt[li], fa);
-      else flash_prefill_tc_kernel<128><<<grid, kFaThreads, FaSmem<128>::kTotal, stream>>>(tm_q, tm_k[li], tm_vt[li], fa);
+      if (d.hd == 256) launch_pdl(flash_prefill_tc_kernel<256>, grid, dim3(kFaThreads), FaSmem<256>::kTotal, stream, tm_q, tm_k[li], tm_vt[li], fa);
+      else launch_pdl(flash_prefill_tc_kernel<128>, grid, dim3(kFaThreads), FaSmem<128>::kTotal, stream, tm_q, tm_k[li], tm_vt[li], fa);
       ++launches;
     } else {
     AttnJob j;

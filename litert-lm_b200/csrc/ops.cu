@@ -114,6 +114,19 @@ __global__ void fill_pages_kernel(const float* __restrict__ src, T* __restrict__
   else dst[off] = __float2bfloat16(src[idx]);
 }
 
+// src [S][hkv][hd] -> transposed bf16 pages [page][hkv][hd][kPage]
+__global__ void fill_pages_vt_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int S, int hkv, int hd) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)S * hkv * hd) return;
+  int e = (int)(idx % hd), h = (int)((idx / hd) % hkv), s = (int)(idx / ((int64_t)hd * hkv));
+  size_t off = (((size_t)(s / kPage) * hkv + h) * hd + e) * kPage + (s % kPage);
+  dst[off] = __float2bfloat16(src[idx]);
+}
+__global__ void scale_to_bf16_kernel(const float* __restrict__ src, __nv_bfloat16* __restrict__ dst, int64_t n, float scale) {
+  int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) dst[i] = __float2bfloat16(src[i] * scale);
+}
+
 }  // namespace b200lm
 
 using namespace b200lm;
@@ -422,6 +435,106 @@ int B200LmOps_Attention(int32_t device, const float* q, const float* k, const fl
   cudaEventDestroy(e0);
   cudaEventDestroy(e1);
   B2_CUDA(cudaMemcpy(out, od.p, (size_t)t * hq * hd * 4, cudaMemcpyDeviceToHost));
+  OPS_END
+}
+
+int B200LmOps_AttentionPrefillTc(int32_t device, const float* q, const float* k, const float* v, int32_t s, int32_t hq,
+                                 int32_t hkv, int32_t hd, int32_t window, int32_t repeat, float* out, float* ms_out,
+                                 char** err) {
+  OPS_BEGIN
+  B2_CHECK(q && k && v && out, kInvalidArgument, "null pointer");
+  B2_CHECK(s > 0 && hq > 0 && hkv > 0 && hq % hkv == 0, kInvalidArgument, "bad shape");
+  const int G = hq / hkv;
+  B2_CHECK(G == 1 || G == 2 || G == 4, kUnimplemented, "GQA group size must be 1, 2 or 4");
+  B2_CHECK(hd == 128 || hd == 256, kUnimplemented, "the tensor-core kernel takes head_dim 128 or 256");
+  need_device(device);
+  // static softmax shift: |q.k| / sqrt(hd) <= max|q| max|k| / sqrt(hd)
+  double mq = 0.0, mk = 0.0;
+  for (int64_t i = 0; i < (int64_t)s * hq; ++i) {
+    double a = 0.0;
+    for (int e = 0; e < hd; ++e) a += (double)q[i * hd + e] * q[i * hd + e];
+    mq = std::max(mq, a);
+  }
+  for (int64_t i = 0; i < (int64_t)s * hkv; ++i) {
+    double a = 0.0;
+    for (int e = 0; e < hd; ++e) a += (double)k[i * hd + e] * k[i * hd + e];
+    mk = std::max(mk, a);
+  }
+  const float bound = (float)(std::sqrt(mq) * std::sqrt(mk) / std::sqrt((double)hd) * 1.02);
+  B2_CHECK(bound <= kFaMaxBound, kFailedPrecondition,
+           "scores can reach " + std::to_string(bound) + ": beyond the static softmax shift of the tensor-core kernel");
+  const int npages = (s + kPage - 1) / kPage;
+  const int tp = (s + 127) / 128 * 128;
+  const size_t pool = (size_t)npages * hkv * kPage * hd;
+  DevBuf src((size_t)s * std::max(hq, hkv) * hd * 4), qb((size_t)tp * hq * hd * 2, true), kb(pool * 2, true),
+      vtb(pool * 2, true), ob((size_t)tp * hq * hd * 2, true), o32((size_t)s * hq * hd * 4), ptab(sizeof(int) * npages),
+      errw(4, true);
+  const int64_t nq = (int64_t)s * hq * hd, nkv = (int64_t)s * hkv * hd;
+  B2_CUDA(cudaMemcpy(src.p, q, (size_t)nq * 4, cudaMemcpyHostToDevice));
+  scale_to_bf16_kernel<<<(unsigned)((nq + 255) / 256), 256>>>(src.as<float>(), qb.as<__nv_bfloat16>(), nq,
+                                                            1.0f / std::sqrt((float)hd));
+  B2_CUDA(cudaDeviceSynchronize());
+  B2_CUDA(cudaMemcpy(src.p, k, (size_t)nkv * 4, cudaMemcpyHostToDevice));
+  fill_pages_kernel<__nv_bfloat16><<<(unsigned)((nkv + 255) / 256), 256>>>(src.as<float>(), kb.as<__nv_bfloat16>(), s, hkv, hd);
+  B2_CUDA(cudaDeviceSynchronize());
+  B2_CUDA(cudaMemcpy(src.p, v, (size_t)nkv * 4, cudaMemcpyHostToDevice));
+  fill_pages_vt_kernel<<<(unsigned)((nkv + 255) / 256), 256>>>(src.as<float>(), vtb.as<__nv_bfloat16>(), s, hkv, hd);
+  B2_CUDA(cudaDeviceSynchronize());
+  std::vector<int> pt(npages);
+  for (int i = 0; i < npages; ++i) pt[i] = i;
+  B2_CUDA(cudaMemcpy(ptab.p, pt.data(), sizeof(int) * npages, cudaMemcpyHostToDevice));
+  CUtensorMap tm_q, tm_k, tm_vt;
+  {
+    cuuint64_t dims[3] = {(cuuint64_t)hd, (cuuint64_t)hq, (cuuint64_t)tp};
+    cuuint64_t str[2] = {(cuuint64_t)hd * 2, (cuuint64_t)hq * hd * 2};
+    cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(128 / G)};
+    tm_q = make_bf16_map(qb.p, 3, dims, str, box);
+    const cuuint64_t rows = (cuuint64_t)npages * hkv * kPage;
+    cuuint64_t kd[2] = {(cuuint64_t)hd, rows};
+    cuuint64_t ks[1] = {(cuuint64_t)hd * 2};
+    cuuint32_t kbx[2] = {64, (cuuint32_t)kFaBN};
+    tm_k = make_bf16_map(kb.p, 2, kd, ks, kbx);
+    cuuint64_t vd[2] = {(cuuint64_t)kPage, (cuuint64_t)npages * hkv * hd};
+    cuuint64_t vs[1] = {(cuuint64_t)kPage * 2};
+    cuuint32_t vbx[2] = {(cuuint32_t)kFaBN, (cuuint32_t)hd};
+    tm_vt = make_bf16_map(vtb.p, 2, vd, vs, vbx);
+  }
+  FaArgs fa{s, 0, hq, hkv, window > 0 ? window : 1 << 30, window > 0 ? 0 : 1, ptab.as<int>(), ob.as<__nv_bfloat16>(), bound,
+            errw.as<int>()};
+  const int TT = 128 / G;
+  dim3 grid((s + TT - 1) / TT, hkv);
+  if (hd == 256)
+    B2_CUDA(cudaFuncSetAttribute(flash_prefill_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<256>::kTotal));
+  else
+    B2_CUDA(cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<128>::kTotal));
+  auto run = [&]() {
+    if (hd == 256) flash_prefill_tc_kernel<256><<<grid, kFaThreads, FaSmem<256>::kTotal>>>(tm_q, tm_k, tm_vt, fa);
+    else flash_prefill_tc_kernel<128><<<grid, kFaThreads, FaSmem<128>::kTotal>>>(tm_q, tm_k, tm_vt, fa);
+  };
+  run();
+  B2_CUDA(cudaGetLastError());
+  B2_CUDA(cudaDeviceSynchronize());
+  if (repeat > 1) {
+    cudaEvent_t e0, e1;
+    B2_CUDA(cudaEventCreate(&e0));
+    B2_CUDA(cudaEventCreate(&e1));
+    B2_CUDA(cudaEventRecord(e0));
+    for (int r = 0; r < repeat; ++r) run();
+    B2_CUDA(cudaEventRecord(e1));
+    B2_CUDA(cudaEventSynchronize(e1));
+    float ms = 0.f;
+    B2_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+    if (ms_out) *ms_out = ms / repeat;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+  } else if (ms_out) {
+    *ms_out = 0.f;
+  }
+  int errv = 0;
+  B2_CUDA(cudaMemcpy(&errv, errw.p, 4, cudaMemcpyDeviceToHost));
+  B2_CHECK(errv == 0, kDeadlineExceeded, "a bounded device-side wait gave up in the attention kernel");
+  bf16_to_f32_kernel<<<(unsigned)((nq + 255) / 256), 256>>>(ob.as<__nv_bfloat16>(), o32.as<float>(), nq);
+  B2_CUDA(cudaMemcpy(out, o32.p, (size_t)nq * 4, cudaMemcpyDeviceToHost));
   OPS_END
 }
 

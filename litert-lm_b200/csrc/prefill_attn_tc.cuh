@@ -88,7 +88,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int G = g.hq / g.hkv;
   const int TT = 128 / G;                       // tokens per tile
-  const int t0 = blockIdx.x * TT, kvh = blockIdx.y;
+  // later query tiles see more keys: they are scheduled first so the longest CTAs do not start last
+  const int t0 = ((int)gridDim.x - 1 - (int)blockIdx.x) * TT, kvh = blockIdx.y;
   constexpr int KB = HD / 64;                   // 64-column blocks of the head dimension
   constexpr uint32_t kTmemCols = HD + 2 * kFaBN <= 256 ? 256 : 512;
   constexpr uint32_t kOCol = 0, kSCol = HD;     // O, then two S buffers of 64 columns
@@ -119,6 +120,8 @@ flash_prefill_tc_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_co
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem = *tmem_slot;
+  pdl_wait();                 // set-up done; Q, K, V below come from the preceding kernel
+  pdl_launch_dependents();
 
   if (warp == 0) {
     // ---- producer

@@ -128,6 +128,9 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tmem_w = tmem_base + kTsTok;
+  // barriers and TMEM are set up: from here on the kernel reads what its predecessor wrote
+  pdl_wait();
+  pdl_launch_dependents();
   if (threadIdx.x == 0) B2_GT(1);
 
   if (warp == 0) {

@@ -39,6 +39,8 @@ pf_embed_norm_kernel(const int* __restrict__ tokens, const uint8_t* __restrict__
                      const float* __restrict__ embed_scale, const float* __restrict__ g, int d,
                      int vocab, float eps, float* __restrict__ xres, __nv_bfloat16* __restrict__ h,
                      int* err) {
+  pdl_wait();
+  pdl_launch_dependents();
   extern __shared__ float pf_sm[];
   __shared__ float scratch[32];
   const int t = blockIdx.x;
@@ -104,6 +106,8 @@ __global__ void __launch_bounds__(THREADS)
 pf_resid_norm_reg_kernel(const float* __restrict__ parts, int nparts, size_t part_stride, int d, float eps,
                          const float* __restrict__ g_post, const float* __restrict__ g_pre,
                          float* __restrict__ xres, __nv_bfloat16* __restrict__ h) {
+  pdl_wait();
+  pdl_launch_dependents();
   __shared__ float red[2][THREADS / 32];
   const int t = blockIdx.x, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int d4 = d / 4;
@@ -212,6 +216,8 @@ pf_kv_append_kernel(ModelDims dm, const float* __restrict__ qkv, int nparts, siz
                     const int* __restrict__ page_table, const float* __restrict__ g_k,
                     const float* __restrict__ cosT, const float* __restrict__ sinT, LayerKv kv,
                     const float* __restrict__ g_q, __nv_bfloat16* __restrict__ qout) {
+  pdl_wait();
+  pdl_launch_dependents();
   constexpr int V = HD >= 64 ? HD / 64 : 1;
   constexpr int half = HD / 2;
   const int lane = threadIdx.x & 31;

@@ -97,6 +97,38 @@ def test_prefill_attention_matches_oracle(pkg, orc, hq, hkv, hd, t, s, qpos0, wi
     assert np.abs(got - want).max() < 2e-4, np.abs(got - want).max()
 
 
+@pytest.mark.parametrize("hq,hkv,hd,s,window", [
+    (4, 1, 256, 300, 0),         # global causal, two pages, ragged last tile
+    (4, 1, 256, 700, 512),       # window 512: tiles fall out of the window on the left
+    (8, 4, 128, 200, 48),        # several kv heads, G = 2, head_dim 128
+    (2, 2, 128, 130, 0),         # no grouping: 128-token tiles, two of them
+    (4, 1, 256, 1023, 0),        # the benchmark's prefill length
+])
+def test_tensor_core_prefill_attention_matches_oracle(pkg, orc, hq, hkv, hd, s, window):
+    """The tcgen05 flash kernel (bf16 operands, bf16 probabilities) against the fp32 oracle on
+    bf16-rounded inputs.  Tolerance: bf16 rounding of P and of the output, 3e-2 absolute on
+    outputs of unit scale."""
+    rng = np.random.Generator(np.random.PCG64(2))
+    q = rng.standard_normal((s, hq, hd), dtype=np.float32)
+    k = rng.standard_normal((s, hkv, hd), dtype=np.float32)
+    v = rng.standard_normal((s, hkv, hd), dtype=np.float32)
+    want = orc.attention(bf16_round(q), bf16_round(k), bf16_round(v), 0, window)
+    got, _ = pkg.ops.attention_prefill_tc(q, k, v, window=window)
+    assert np.isfinite(got).all()
+    err = np.abs(got - want).max()
+    assert err < 3e-2, err
+    # the first token attends to itself only: its output is v[0] (bf16-rounded twice)
+    assert np.abs(got[0] - np.repeat(bf16_round(v[0]), hq // hkv, axis=0)).max() < 2e-2
+
+
+def test_tensor_core_prefill_attention_rejects_unbounded_scores(pkg):
+    q = np.full((64, 4, 256), 3.0, dtype=np.float32)
+    k = np.full((64, 1, 256), 3.0, dtype=np.float32)
+    with pytest.raises(pkg.StatusError) as e:
+        pkg.ops.attention_prefill_tc(q, k, k)
+    assert e.value.code == pkg.FAILED_PRECONDITION
+
+
 @pytest.mark.parametrize("hq,hkv,hd,batch,s,window,kv_bf16,nsplit", [
     (4, 1, 256, 1, 1100, 0, False, 32), (4, 1, 256, 1, 1100, 512, False, 8), (4, 1, 256, 4, 4096, 0, True, 16),
     (8, 4, 128, 3, 300, 48, True, 4), (4, 1, 32, 2, 7, 8, False, 2), (4, 1, 256, 2, 5, 0, False, 32),
