@@ -54,7 +54,10 @@ int B200LmOps_GemmGegluW4(int32_t device, int32_t mode, const uint8_t* gate_pack
  * (window <= 0: global).  No QK-norm, no RoPE (raw q/k, as the attention-only
  * micro-benchmark specifies).  nsplit > 1 runs the split-KV decode kernel plus
  * the log-sum-exp combine (T is then a batch of independent single-token
- * queries all at position S - 1); nsplit == 1 runs the prefill kernel. */
+ * queries all at position S - 1); nsplit == 1 runs the prefill kernel.
+ * kv_bf16: bit 0 = bf16 pages (else fp32); bit 1 (decode only) = every query
+ * gets its own physical copy of the cache and its own page table, i.e. a
+ * batch of independent sequences instead of queries sharing one cache. */
 int B200LmOps_Attention(int32_t device, const float* q, const float* k, const float* v, int32_t t, int32_t s,
                         int32_t hq, int32_t hkv, int32_t hd, int32_t qpos0, int32_t window,
                         int32_t kv_bf16, int32_t nsplit, int32_t repeat, float* out, float* ms_out,

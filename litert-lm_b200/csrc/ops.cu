@@ -355,31 +355,40 @@ int B200LmOps_Attention(int32_t device, const float* q, const float* k, const fl
   ModelDims dm{};
   dm.hq = hq; dm.hkv = hkv; dm.hd = hd; dm.d = 64; dm.ffn = 64;
   dm.window = window > 0 ? window : 1 << 30;
-  dm.kv_dtype = kv_bf16 ? 1 : 0;
+  dm.kv_dtype = (kv_bf16 & 1) ? 1 : 0;
   dm.eps = 1e-6f;
   const bool decode = nsplit > 1;
+  const bool priv = decode && (kv_bf16 & 2);     // every query reads its own physical copy of the cache
+  kv_bf16 &= 1;
   const int npages = (s + kPage - 1) / kPage;
   dm.max_ctx = npages * kPage;
   const size_t esz = kv_bf16 ? 2 : 4;
   const size_t pool = (size_t)npages * hkv * kPage * hd;
-  DevBuf kp(pool * esz, true), vp(pool * esz, true), src((size_t)s * hkv * hd * 4);
+  const int ncopies = priv ? t : 1;
+  B2_CHECK((double)pool * esz * 2 * ncopies <= 16e9, kInvalidArgument, "private caches would exceed 16 GB");
+  DevBuf kp(pool * esz * ncopies, true), vp(pool * esz * ncopies, true), src((size_t)s * hkv * hd * 4);
   int64_t nkv = (int64_t)s * hkv * hd;
   for (int pass = 0; pass < 2; ++pass) {
     B2_CUDA(cudaMemcpy(src.p, pass ? v : k, (size_t)nkv * 4, cudaMemcpyHostToDevice));
     void* dstp = pass ? vp.p : kp.p;
     if (kv_bf16) fill_pages_kernel<__nv_bfloat16><<<(unsigned)((nkv + 255) / 256), 256>>>(src.as<float>(), reinterpret_cast<__nv_bfloat16*>(dstp), s, hkv, hd);
     else fill_pages_kernel<float><<<(unsigned)((nkv + 255) / 256), 256>>>(src.as<float>(), reinterpret_cast<float*>(dstp), s, hkv, hd);
+    for (int c = 1; c < ncopies; ++c)
+      B2_CUDA(cudaMemcpyAsync(reinterpret_cast<unsigned char*>(dstp) + (size_t)c * pool * esz, dstp, pool * esz,
+                              cudaMemcpyDeviceToDevice, 0));
+    B2_CUDA(cudaDeviceSynchronize());
   }
   // queries laid out like a QKV projection row: [q heads | k | v]; only q is read
   const int nqkv = (hq + 2 * hkv) * hd;
   std::vector<float> rows((size_t)t * nqkv, 0.f);
   for (int i = 0; i < t; ++i) memcpy(rows.data() + (size_t)i * nqkv, q + (size_t)i * hq * hd, sizeof(float) * hq * hd);
-  DevBuf qd(rows.size() * 4), ptab(sizeof(int) * npages), posd(sizeof(int) * t), errw(4, true);
+  DevBuf qd(rows.size() * 4), ptab(sizeof(int) * npages * ncopies), posd(sizeof(int) * t), errw(4, true);
   B2_CUDA(cudaMemcpy(qd.p, rows.data(), rows.size() * 4, cudaMemcpyHostToDevice));
-  std::vector<int> pt(npages), pos(t);
-  for (int i = 0; i < npages; ++i) pt[i] = i;
+  std::vector<int> pt((size_t)npages * ncopies), pos(t);
+  for (int c = 0; c < ncopies; ++c)
+    for (int i = 0; i < npages; ++i) pt[(size_t)c * npages + i] = c * npages + i;
   for (int i = 0; i < t; ++i) pos[i] = decode ? s - 1 : qpos0 + i;
-  B2_CUDA(cudaMemcpy(ptab.p, pt.data(), sizeof(int) * npages, cudaMemcpyHostToDevice));
+  B2_CUDA(cudaMemcpy(ptab.p, pt.data(), sizeof(int) * pt.size(), cudaMemcpyHostToDevice));
   B2_CUDA(cudaMemcpy(posd.p, pos.data(), sizeof(int) * t, cudaMemcpyHostToDevice));
   DevBuf po((size_t)t * hkv * nsplit * G * hd * 4, true), pml((size_t)t * hkv * nsplit * G * 2 * 4, true);
   DevBuf od((size_t)t * hq * hd * 4, true);
@@ -389,7 +398,7 @@ int B200LmOps_Attention(int32_t device, const float* q, const float* k, const fl
   j.pos = posd.as<int>();
   j.page_table = ptab.as<int>();
   j.pages_per_seq = npages;
-  j.seq_stride = 0;
+  j.seq_stride = priv ? 1 : 0;
   j.is_global = window > 0 ? 0 : 1;
   j.nsplit = nsplit;
   j.appended = 1;

@@ -143,3 +143,6 @@ def test_split_kv_decode_attention_matches_oracle(pkg, orc, hq, hkv, hd, batch, 
     want = np.concatenate([orc.attention(q[i:i + 1], kk, vv, s - 1, window) for i in range(batch)])
     got, _ = pkg.ops.attention(q, k, v, window=window, kv_bf16=kv_bf16, nsplit=nsplit)
     assert np.abs(got - want).max() < 2e-4, np.abs(got - want).max()
+    # a batch of independent sequences (own cache copy and page table each) gives the same rows, bit for bit
+    own, _ = pkg.ops.attention(q, k, v, window=window, kv_bf16=kv_bf16, nsplit=nsplit, private_caches=True)
+    assert np.array_equal(own, got)
