@@ -50,6 +50,9 @@ typedef struct B200LmConfig {
   int32_t prefill_gemm;    /* B200LM_GEMM_* */
   int32_t reserved0;
   void* stream;            /* cudaStream_t to run on, or NULL for an own stream */
+  int32_t n_sessions;      /* sessions held by this executor, 1..4 (0 = 1); see
+                              B200Lm_DecodeTokensBatch */
+  int32_t reserved1;
 } B200LmConfig;
 
 /* Replaces LlmLiteRtCompiledModelExecutor::Create
@@ -93,6 +96,25 @@ int B200Lm_DecodeToken(B200LmExecutor* e, int32_t* out_id, char** err);
  * trip per step; ids come back at the end.  Equivalent to n_steps calls of
  * B200Lm_DecodeToken. */
 int B200Lm_DecodeTokens(B200LmExecutor* e, int32_t n_steps, int32_t* out_ids, char** err);
+
+/* Several sessions in one executor.  No counterpart in the reference, whose
+ * engine gives every session the one executor in turn (runtime/core/
+ * session_basic.cc:67-72).  An executor created with n_sessions = B holds B
+ * independent sessions over one weight copy: each has its own KV pages, step
+ * counter and pending id.  B200Lm_SelectSession makes one of them the session
+ * that Prefill / DecodeLogits / DecodeToken(s) / Reset / GetCurrentStep /
+ * GetLastPrefillPlan / ReadKvRow act on (session 0 after Create);
+ * B200Lm_PrefillSession is Select + Prefill.  B200Lm_DecodeTokensBatch advances
+ * ALL sessions by n_steps greedy steps in lockstep, reading the weights once
+ * per step for the whole batch; out_ids is [n_steps][n_sessions].  Every
+ * session must have a pending id (i.e. have been prefilled).  With three or
+ * four sessions the decode activations are quantised to two int8 terms
+ * instead of three (relative error 6e-5 instead of 5e-7). */
+int B200Lm_SelectSession(B200LmExecutor* e, int32_t session, char** err);
+int B200Lm_GetNumSessions(B200LmExecutor* e, int32_t* out, char** err);
+int B200Lm_PrefillSession(B200LmExecutor* e, int32_t session, const int32_t* ids, int32_t n,
+                          int32_t wait_for_completion, const volatile int32_t* cancel_or_null, char** err);
+int B200Lm_DecodeTokensBatch(B200LmExecutor* e, int32_t n_steps, int32_t* out_ids, char** err);
 
 /* Replaces Reset() (llm_litert_compiled_model_executor.cc:568-574): rewinds the
  * counters, leaves the cache contents in place. */

@@ -47,7 +47,7 @@ class StatusError(RuntimeError):
 class B200LmConfig(C.Structure):
     _fields_ = [("struct_size", C.c_int32), ("device", C.c_int32), ("max_num_tokens", C.c_int32),
                 ("decode_mode", C.c_int32), ("prefill_gemm", C.c_int32), ("reserved0", C.c_int32),
-                ("stream", C.c_void_p)]
+                ("stream", C.c_void_p), ("n_sessions", C.c_int32), ("reserved1", C.c_int32)]
 
 
 _lib: Optional[C.CDLL] = None
@@ -55,7 +55,8 @@ _lib: Optional[C.CDLL] = None
 _EXEC_SYMBOLS = ["B200Lm_Create", "B200Lm_CreateShared", "B200Lm_Destroy", "B200Lm_Prefill", "B200Lm_DecodeLogits",
                  "B200Lm_DecodeToken", "B200Lm_DecodeTokens", "B200Lm_Reset", "B200Lm_GetVocabSize",
                  "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_BackendName", "B200Lm_Synchronize",
-                 "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount", "B200Lm_TraceDecodeStep"]
+                 "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount", "B200Lm_TraceDecodeStep",
+                 "B200Lm_SelectSession", "B200Lm_GetNumSessions", "B200Lm_PrefillSession", "B200Lm_DecodeTokensBatch"]
 _OPS_SYMBOLS = ["B200LmOps_RepackW4T", "B200LmOps_RepackW4G", "B200LmOps_UnpackW4", "B200LmOps_GemvW4",
                 "B200LmOps_GemmW4", "B200LmOps_GemmGegluW4", "B200LmOps_Attention", "B200LmOps_AttentionPrefillTc",
                 "B200LmOps_AttentionDecodeStatic"]
@@ -88,6 +89,10 @@ def load_library() -> C.CDLL:
         "B200Lm_ReadKvRow": [vp, i32, i32, i32, i32, vp, vp, vp, errp],
         "B200Lm_GetLaunchCount": [vp, vp, errp],
         "B200Lm_TraceDecodeStep": [vp, vp, vp, i64, vp, vp, vp, errp],
+        "B200Lm_SelectSession": [vp, i32, errp],
+        "B200Lm_GetNumSessions": [vp, vp, errp],
+        "B200Lm_PrefillSession": [vp, i32, vp, i32, i32, vp, errp],
+        "B200Lm_DecodeTokensBatch": [vp, i32, vp, errp],
         "B200LmOps_RepackW4T": [vp, i64, i64, vp, errp],
         "B200LmOps_RepackW4G": [vp, i64, i64, vp, errp],
         "B200LmOps_UnpackW4": [i32, vp, i64, i64, vp, errp],
@@ -144,10 +149,10 @@ class B200LlmExecutor:
 
     def __init__(self, model, device: int = 0, max_num_tokens: int = 0, decode_mode: int = DECODE_AUTO,
                  prefill_gemm: int = GEMM_AUTO, stream: int = 0, reversed_pages: bool = False,
-                 _shared_from: "Optional[B200LlmExecutor]" = None) -> None:
+                 n_sessions: int = 1, _shared_from: "Optional[B200LlmExecutor]" = None) -> None:
         self._h = C.c_void_p()
         cfg = B200LmConfig(C.sizeof(B200LmConfig), device, max_num_tokens, decode_mode, prefill_gemm,
-                           1 if reversed_pages else 0, stream or None)
+                           1 if reversed_pages else 0, stream or None, n_sessions, 0)
         if _shared_from is not None:
             _call("B200Lm_CreateShared", _shared_from._h, C.byref(cfg), C.byref(self._h))
         elif isinstance(model, (bytes, bytearray, memoryview)):
@@ -189,6 +194,27 @@ class B200LlmExecutor:
 
     def Reset(self) -> None:
         _call("B200Lm_Reset", self._h)
+
+    # -- several sessions in one executor (no reference counterpart) -----------------------
+    def SelectSession(self, session: int) -> None:
+        """Makes `session` the one the single-session calls act on."""
+        _call("B200Lm_SelectSession", self._h, session)
+
+    def GetNumSessions(self) -> int:
+        v = C.c_int32()
+        _call("B200Lm_GetNumSessions", self._h, C.byref(v))
+        return v.value
+
+    def PrefillSession(self, session: int, ids: Sequence[int], wait_for_completion: bool = True) -> None:
+        a = np.ascontiguousarray(ids, dtype=np.int32).ravel()
+        _call("B200Lm_PrefillSession", self._h, session, _ptr(a) if a.size else None, a.size, int(wait_for_completion),
+              None)
+
+    def DecodeTokensBatch(self, n_steps: int) -> np.ndarray:
+        """All sessions take n_steps greedy steps in lockstep; returns ids [n_steps, n_sessions]."""
+        out = np.empty((max(n_steps, 0), self.GetNumSessions()), dtype=np.int32)
+        _call("B200Lm_DecodeTokensBatch", self._h, n_steps, _ptr(out))
+        return out
 
     def GetVocabSize(self) -> int:
         return self._vocab

@@ -353,7 +353,12 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   const int esz = d.kv_dtype == 0 ? 4 : 2;
   // ---- paged KV cache
   e->pages_per_seq = (d.max_ctx + kPage - 1) / kPage;
-  size_t pool = (size_t)e->pages_per_seq * d.hkv * kPage * d.hd;
+  e->n_sessions = cfg.n_sessions > 0 ? cfg.n_sessions : 1;
+  B2_CHECK(e->n_sessions <= kMaxCols, kInvalidArgument,
+           "n_sessions exceeds the " + std::to_string(kMaxCols) + " sessions one decode step can carry");
+  e->parked.resize(e->n_sessions);
+  const int total_pages = e->pages_per_seq * e->n_sessions;
+  size_t pool = (size_t)total_pages * d.hkv * kPage * d.hd;
   e->kv_host.resize(d.n_layers);
   // tensor-core prefill attention: head_dim 128 / 256, and every layer's score bound small enough
   e->attn_tc = e->prefill_gemm == B200LM_GEMM_TCGEN05 && (d.hd == 128 || d.hd == 256);
@@ -371,11 +376,14 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   LayerKv* kvd = reinterpret_cast<LayerKv*>(e->alloc(sizeof(LayerKv) * d.n_layers, false));
   B2_CUDA(cudaMemcpy(kvd, e->kv_host.data(), sizeof(LayerKv) * d.n_layers, cudaMemcpyHostToDevice));
   e->kv_dev = kvd;
-  e->page_table_host.resize(e->pages_per_seq);
-  for (int i = 0; i < e->pages_per_seq; ++i)
-    e->page_table_host[i] = (cfg.reserved0 & 1) ? e->pages_per_seq - 1 - i : i;   // bit 0: reversed page order
-  int* ptd = reinterpret_cast<int*>(e->alloc(sizeof(int) * e->pages_per_seq, false));
-  B2_CUDA(cudaMemcpy(ptd, e->page_table_host.data(), sizeof(int) * e->pages_per_seq, cudaMemcpyHostToDevice));
+  // one page-table row per session, each over its own block of physical pages
+  e->page_table_host.resize(total_pages);
+  for (int sn = 0; sn < e->n_sessions; ++sn)
+    for (int i = 0; i < e->pages_per_seq; ++i)
+      e->page_table_host[(size_t)sn * e->pages_per_seq + i] =
+          sn * e->pages_per_seq + ((cfg.reserved0 & 1) ? e->pages_per_seq - 1 - i : i);   // bit 0: reversed page order
+  int* ptd = reinterpret_cast<int*>(e->alloc(sizeof(int) * total_pages, false));
+  B2_CUDA(cudaMemcpy(ptd, e->page_table_host.data(), sizeof(int) * total_pages, cudaMemcpyHostToDevice));
   e->page_table_dev = ptd;
   // ---- decode buffers
   DecodeArgs& a = e->dargs;
@@ -428,14 +436,15 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   a.step_capacity = d.max_ctx;
   a.step_tokens = reinterpret_cast<int*>(e->alloc(sizeof(int) * a.step_capacity * kMaxCols, true));
   a.advance = 1;
-  e->dec_smem = dec_smem_bytes(d, a.ncols);
+  // the one-kernel-per-phase fallback drives one session; the persistent kernels carry all of them
+  e->dec_smem = dec_smem_bytes(d, e->decode_mode == B200LM_DECODE_PERSISTENT ? 1 : e->n_sessions);
   B2_CHECK(e->dec_smem <= (size_t)prop.sharedMemPerBlockOptin, kUnimplemented,
            "decode kernels need more shared memory than the device offers");
   B2_CUDA(cudaFuncSetAttribute(decode_phase_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->dec_smem));
   B2_CUDA(cudaFuncSetAttribute(decode_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->dec_smem));
   if (e->decode_mode == B200LM_DECODE_PERSISTENT) {
     // staging halves take what shared memory the activation staging leaves, up to 96 KiB each
-    size_t fixed = stream_fixed_bytes(d, a.ncols);
+    size_t fixed = stream_fixed_bytes(d, e->n_sessions);
     long room = ((long)prop.sharedMemPerBlockOptin - (long)fixed - 2048) / 2;   // margin: static shared memory
     int half = (int)std::min<long>(room, 96 * 1024) / 1024 * 1024;
     bool ok = half > 0 && stream_model_fits(d, a.o_slices, a.down_slices, half) && prop.cooperativeLaunch;
@@ -451,6 +460,8 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
     }
     if (!ok) e->decode_mode = B200LM_DECODE_PHASE_KERNELS;
   }
+  B2_CHECK(e->n_sessions == 1 || e->decode_mode != B200LM_DECODE_PHASE_KERNELS, kUnimplemented,
+           "several sessions per executor need a persistent decode kernel, which this model / device does not fit");
   if (e->decode_mode == B200LM_DECODE_PERSISTENT_BASIC) {
     int occ = 0;
     B2_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, decode_persistent_kernel, kDecThreads, e->dec_smem));
@@ -476,14 +487,14 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
       cuuint32_t box[3] = {64, (cuuint32_t)G, (cuuint32_t)(128 / G)};
       e->tm_q = make_bf16_map(e->pf_q, 3, dims, str, box);
     }
-    const cuuint64_t rows = (cuuint64_t)e->pages_per_seq * d.hkv * kPage;
+    const cuuint64_t rows = (cuuint64_t)total_pages * d.hkv * kPage;
     for (int i = 0; i < d.n_layers; ++i) {
       const void* kbase = d.kv_dtype == 0 ? (const void*)e->kv_host[i].k16 : (const void*)e->kv_host[i].k;
       cuuint64_t kd[2] = {(cuuint64_t)d.hd, rows};
       cuuint64_t ks[1] = {(cuuint64_t)d.hd * 2};
       cuuint32_t kb[2] = {64, (cuuint32_t)kFaBN};
       e->tm_k.push_back(make_bf16_map(kbase, 2, kd, ks, kb));
-      cuuint64_t vd[2] = {(cuuint64_t)kPage, (cuuint64_t)e->pages_per_seq * d.hkv * d.hd};
+      cuuint64_t vd[2] = {(cuuint64_t)kPage, (cuuint64_t)total_pages * d.hkv * d.hd};
       cuuint64_t vs[1] = {(cuuint64_t)kPage * 2};
       cuuint32_t vb[2] = {(cuuint32_t)kFaBN, (cuuint32_t)d.hd};
       e->tm_vt.push_back(make_bf16_map(e->kv_host[i].v16, 2, vd, vs, vb));
@@ -569,6 +580,7 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
   B2_CUDA(cudaMemcpyAsync(pf_tokens, pin_ints, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
   h2d_bytes += sizeof(int) * (size_t)T;
   int* err = &dargs.st->err;
+  const int* ptab = page_table_dev + (size_t)active * pages_per_seq;     // the active session's pages
   const size_t sm_d = sizeof(float) * d.d;
   pf_embed_norm_kernel<<<T, kPfThreads, sm_d, stream>>>(pf_tokens, model->embed_rows, model->embed_scale,
                                                         model->layers_host[0].g_pre_attn, d.d, d.vocab, d.eps,
@@ -593,11 +605,11 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
     launch_gemm(stream, mode, tm_h, pf_h, L.wqkv, L.sqkv, Gm.wqkv, Gm.sqkv, T, d.nqkv(), d.d, ks_q, false, qkv_buf,
                 nullptr, err, &launches);
     __nv_bfloat16* qout = attn_tc ? pf_q : nullptr;
-    if (d.kv_dtype == 0) launch_kv_append<float>(stream, d, T, qkv_buf, ks_q, start, page_table_dev, L, cosT, sinT, kv_host[li], qout);
-    else launch_kv_append<__nv_bfloat16>(stream, d, T, qkv_buf, ks_q, start, page_table_dev, L, cosT, sinT, kv_host[li], qout);
+    if (d.kv_dtype == 0) launch_kv_append<float>(stream, d, T, qkv_buf, ks_q, start, ptab, L, cosT, sinT, kv_host[li], qout);
+    else launch_kv_append<__nv_bfloat16>(stream, d, T, qkv_buf, ks_q, start, ptab, L, cosT, sinT, kv_host[li], qout);
     ++launches;
     if (attn_tc) {
-      FaArgs fa{T, start, d.hq, d.hkv, d.window, L.is_global, page_table_dev, pf_attn, model->attn_bound[li], err};
+      FaArgs fa{T, start, d.hq, d.hkv, d.window, L.is_global, ptab, pf_attn, model->attn_bound[li], err};
       const int TT = 128 / d.group();
       dim3 grid((T + TT - 1) / TT, d.hkv);
       if (d.hd == 256) launch_pdl(flash_prefill_tc_kernel<256>, grid, dim3(kFaThreads), FaSmem<256>::kTotal, stream, tm_q, tm_k[li], tm_vt[li], fa);
@@ -609,7 +621,7 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
     j.qkv = pf_qkv;
     j.pos = nullptr;
     j.pos0 = start;
-    j.page_table = page_table_dev;
+    j.page_table = ptab;
     j.pages_per_seq = pages_per_seq;
     j.seq_stride = 0;
     j.is_global = L.is_global;
@@ -692,11 +704,20 @@ void Executor::prefill(const int* ids, int n, bool wait, const volatile int* can
 
 // -------------------------------------------------------------------- decode
 
-void Executor::launch_decode_steps(int nsteps) {
+// ncols sessions advance together, starting at `first_session` (default: the active one alone).
+void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
   const ModelDims& d = model->dims;
   const int ncta = n_sms;
+  if (first_session < 0) first_session = active;
   if (decode_mode == B200LM_DECODE_PERSISTENT || decode_mode == B200LM_DECODE_PERSISTENT_BASIC) {
     DecodeArgs a = dargs;
+    a.ncols = ncols;
+    a.nterms = ncols * 3 <= kQCols ? 3 : kQCols / ncols;      // int8 terms per activation: 3, or 2 with 3-4 sessions
+    a.page_table = page_table_dev + (size_t)first_session * pages_per_seq;
+    // one CTA per (session, kv head, split)
+    const int cap = std::max(1, ncta / (ncols * d.hkv));
+    a.n_attn_splits_local = std::min(a.n_attn_splits_local, cap);
+    a.n_attn_splits_global = std::min(a.n_attn_splits_global, cap);
     unsigned epoch0 = barrier_epoch;
     if (decode_mode == B200LM_DECODE_PERSISTENT) {
       int half = stream_half;
@@ -712,6 +733,8 @@ void Executor::launch_decode_steps(int nsteps) {
     launches += 1;
     return;
   }
+  B2_CHECK(ncols == 1, kFailedPrecondition, "batched decode needs a persistent decode mode");
+  B2_CHECK(n_sessions == 1, kFailedPrecondition, "several sessions per executor need a persistent decode mode");
   if (!graph_exec) {
     cudaGraph_t graph;
     B2_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
@@ -728,15 +751,17 @@ void Executor::launch_decode_steps(int nsteps) {
   launches += (int64_t)nsteps * (5 * d.n_layers + 2);
 }
 
-void Executor::push_decode_state(int token, int pos) {
+void Executor::push_decode_state(const int* tokens, const int* pos, int ncols) {
   DecodeState* ps = pin_state;
   memset(ps, 0, sizeof(DecodeState));
-  ps->token[0] = token;
-  ps->pos[0] = pos;
+  for (int c = 0; c < ncols; ++c) {
+    ps->token[c] = tokens[c];
+    ps->pos[c] = pos[c];
+  }
   // token, pos, out_token: the first three arrays; err / barrier / steps_done handled separately
   B2_CUDA(cudaMemcpyAsync(dargs.st, ps, offsetof(DecodeState, err), cudaMemcpyHostToDevice, stream));
   B2_CUDA(cudaMemsetAsync(&dargs.st->steps_done, 0, sizeof(int), stream));
-  h2d_bytes += 2 * sizeof(int);
+  h2d_bytes += 2 * sizeof(int) * (size_t)ncols;
 }
 
 int Executor::take_decode_id(const int* id_or_null) {
@@ -752,7 +777,7 @@ void Executor::decode_logits(const int* id_or_null, float* host_logits) {
   B2_CHECK(host_logits != nullptr, kInvalidArgument, "logits destination is null");
   B2_CUDA(cudaSetDevice(device));
   int id = take_decode_id(id_or_null);
-  push_decode_state(id, current_step);
+  push_decode_state(&id, &current_step, 1);
   launch_decode_steps(1);
   const size_t nb = sizeof(float) * (size_t)model->dims.vocab;
   B2_CUDA(cudaMemcpyAsync(pin_logits, dargs.logits, nb, cudaMemcpyDeviceToHost, stream));
@@ -767,20 +792,56 @@ void Executor::decode_tokens(int nsteps, int* out_ids) {
   B2_CUDA(cudaSetDevice(device));
   B2_CHECK(current_step + nsteps <= max_num_tokens, kInvalidArgument, "Maximum kv-cache size reached.");
   int id = take_decode_id(nullptr);
-  push_decode_state(id, current_step);
+  push_decode_state(&id, &current_step, 1);
   launch_decode_steps(nsteps);
   int* dst = pin_ints + t_pad;
-  B2_CUDA(cudaMemcpyAsync(dst, dargs.step_tokens, sizeof(int) * (size_t)nsteps * dargs.ncols, cudaMemcpyDeviceToHost,
-                          stream));
+  B2_CUDA(cudaMemcpyAsync(dst, dargs.step_tokens, sizeof(int) * (size_t)nsteps, cudaMemcpyDeviceToHost, stream));
   d2h_bytes += sizeof(int) * (size_t)nsteps;
   check_device_error("Decode");
   for (int s = 0; s < nsteps; ++s) {
-    int t = dst[(size_t)s * dargs.ncols];
+    int t = dst[s];
     if (t < 0) t = 0;   // "The sampled token is casted to 0 to avoid crash."
     if (out_ids) out_ids[s] = t;
     next_input_token = t;
   }
   current_step += nsteps;
+}
+
+// All sessions take `nsteps` greedy steps together: one pass over the weights per step.
+void Executor::decode_tokens_batch(int nsteps, int* out_ids) {
+  B2_CHECK(nsteps > 0, kInvalidArgument, "n_steps must be positive");
+  B2_CUDA(cudaSetDevice(device));
+  const int keep = active;
+  int tok[kMaxCols], pos[kMaxCols];
+  for (int sn = 0; sn < n_sessions; ++sn) {        // validate every session before any state changes
+    const int pending = sn == active ? next_input_token : parked[sn].next_input_token;
+    const int step = sn == active ? current_step : parked[sn].current_step;
+    B2_CHECK(pending != -1, kInvalidArgument, "No id available to be decoded (session " + std::to_string(sn) + ").");
+    B2_CHECK(step + nsteps <= max_num_tokens, kInvalidArgument, "Maximum kv-cache size reached.");
+  }
+  for (int sn = 0; sn < n_sessions; ++sn) {
+    select_session(sn);
+    tok[sn] = take_decode_id(nullptr);
+    pos[sn] = current_step;
+  }
+  push_decode_state(tok, pos, n_sessions);
+  launch_decode_steps(nsteps, n_sessions, 0);
+  int* dst = pin_ints + t_pad;
+  B2_CUDA(cudaMemcpyAsync(dst, dargs.step_tokens, sizeof(int) * (size_t)nsteps * n_sessions, cudaMemcpyDeviceToHost,
+                          stream));
+  d2h_bytes += sizeof(int) * (size_t)nsteps * n_sessions;
+  check_device_error("Decode");
+  for (int sn = 0; sn < n_sessions; ++sn) {
+    select_session(sn);
+    for (int s = 0; s < nsteps; ++s) {
+      int t = dst[(size_t)s * n_sessions + sn];
+      if (t < 0) t = 0;
+      if (out_ids) out_ids[(size_t)s * n_sessions + sn] = t;
+      next_input_token = t;
+    }
+    current_step += nsteps;
+  }
+  select_session(keep);
 }
 
 void Executor::trace_decode_step(int* out_id, long long* stamps, long long capacity, int* n_barriers, int* n_cta,
@@ -819,13 +880,24 @@ void Executor::reset() {
   next_input_token = -1;
 }
 
+void Executor::select_session(int session) {
+  B2_CHECK(session >= 0 && session < n_sessions, kInvalidArgument,
+           "session " + std::to_string(session) + " out of range (the executor has " + std::to_string(n_sessions) + ")");
+  if (session == active) return;
+  parked[active] = SessionState{current_step, next_input_token, last_plan};
+  current_step = parked[session].current_step;
+  next_input_token = parked[session].next_input_token;
+  last_plan = parked[session].last_plan;
+  active = session;
+}
+
 void Executor::read_kv_row(int layer, int is_v, int kv_head, int pos, float* out, int* page, int* slot) {
   const ModelDims& d = model->dims;
   B2_CHECK(layer >= 0 && layer < d.n_layers && kv_head >= 0 && kv_head < d.hkv && pos >= 0 && pos < d.max_ctx,
            kInvalidArgument, "KV row index out of range");
   B2_CUDA(cudaSetDevice(device));
   B2_CUDA(cudaStreamSynchronize(stream));
-  int pg = page_table_host[pos / kPage], sl = pos % kPage;
+  int pg = page_table_host[(size_t)active * pages_per_seq + pos / kPage], sl = pos % kPage;
   size_t off = (((size_t)pg * d.hkv + kv_head) * kPage + sl) * d.hd;
   const void* base = is_v ? kv_host[layer].v : kv_host[layer].k;
   if (d.kv_dtype == 0) {
@@ -965,6 +1037,36 @@ int B200Lm_DecodeTokens(B200LmExecutor* e, int32_t n_steps, int32_t* out_ids, ch
   B2_API_BEGIN
   B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
   e->impl->decode_tokens(n_steps, out_ids);
+  B2_API_END
+}
+
+int B200Lm_PrefillSession(B200LmExecutor* e, int32_t session, const int32_t* ids, int32_t n, int32_t wait_for_completion,
+                          const volatile int32_t* cancel_or_null, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
+  e->impl->select_session(session);
+  e->impl->prefill(ids, n, wait_for_completion != 0, reinterpret_cast<const volatile int*>(cancel_or_null));
+  B2_API_END
+}
+
+int B200Lm_DecodeTokensBatch(B200LmExecutor* e, int32_t n_steps, int32_t* out_ids, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
+  e->impl->decode_tokens_batch(n_steps, out_ids);
+  B2_API_END
+}
+
+int B200Lm_SelectSession(B200LmExecutor* e, int32_t session, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl, kInvalidArgument, "null handle");
+  e->impl->select_session(session);
+  B2_API_END
+}
+
+int B200Lm_GetNumSessions(B200LmExecutor* e, int32_t* out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out, kInvalidArgument, "null argument");
+  *out = e->impl->n_sessions;
   B2_API_END
 }
 

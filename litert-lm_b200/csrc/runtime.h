@@ -59,6 +59,9 @@ class Executor {
   void decode_logits(const int* id_or_null, float* host_logits);
   void decode_tokens(int nsteps, int* out_ids);
   void reset();
+  // several sessions in one executor (own KV pages, step counter and pending id each; one weight copy)
+  void select_session(int session);                 // the calls above then act on that session
+  void decode_tokens_batch(int nsteps, int* out_ids /* [nsteps][n_sessions] */);
   void check_device_error(const char* where);
   void trace_decode_step(int* out_id, long long* stamps, long long capacity, int* n_barriers, int* n_cta, int* khz);
   void read_kv_row(int layer, int is_v, int kv_head, int pos, float* out, int* page, int* slot);
@@ -74,6 +77,14 @@ class Executor {
   int current_step = 0;
   int next_input_token = -1;
   std::vector<std::pair<int, int>> last_plan;
+  int n_sessions = 1;
+  int active = 0;                                   // session the three fields above belong to
+  struct SessionState {
+    int current_step = 0;
+    int next_input_token = -1;
+    std::vector<std::pair<int, int>> last_plan;
+  };
+  std::vector<SessionState> parked;                 // state of the sessions that are not active
   int64_t launches = 0;
   size_t h2d_bytes = 0, d2h_bytes = 0;
 
@@ -82,8 +93,8 @@ class Executor {
   void* alloc(size_t bytes, bool zero);
   void run_prefill_chunk(const int* tokens, int T, int start);
   void prefill_group(const int* ids, int len);
-  void launch_decode_steps(int nsteps);
-  void push_decode_state(int token, int pos);
+  void launch_decode_steps(int nsteps, int ncols = 1, int first_session = -1);
+  void push_decode_state(const int* tokens, const int* pos, int ncols);
   int take_decode_id(const int* id_or_null);
 
   std::vector<void*> allocations;
