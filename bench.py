@@ -400,7 +400,7 @@ def main() -> None:
                      "frac_of_nominal_8TBs": achieved_gbs / 8000.0},
     }
     if not args.no_cpu_baseline and world == 1:
-        pt, ds = 32, 8
+        pt, ds = 256, 256        # about 10-15 s of CPU work on 16 cores
         t0 = time.perf_counter()
         p, d = cpu_sample(rec, cfg, pt, ds)
         line["cpu_baseline"] = {"value": d, "unit": "tok/s", "cores": host_threads(), "kind": "port",
