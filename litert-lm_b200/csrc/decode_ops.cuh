@@ -38,7 +38,7 @@ struct LayerWeights {
   const float *g_pre_attn, *g_post_attn, *g_pre_ffn, *g_post_ffn, *g_q, *g_k;
   int is_global;
   float gmax_pre_attn, gmax_pre_ffn;   // max |gain| of the two pre-norm gain vectors
-  int pad;
+  float attn_bound;                    // |q.k| / sqrt(hd) <= attn_bound after QK-RMSNorm: sqrt(hd) max|g_q| max|g_k|
 };
 
 struct LayerKv {

@@ -51,7 +51,7 @@ struct StreamCursor {
 struct FillDesc {      // published by the producer for the consumers of one fill
   int ph, layer, round, valid;
   int ta, ntile, ktn, has_gains;          // GEMV fills
-  int col, kvh, split, nsplit, k0, npre, is_global, pad;   // attention fills
+  int col, kvh, split, nsplit, k0, npre, is_global, pos;   // attention fills
 };
 
 struct StreamCtx {
@@ -79,7 +79,7 @@ __host__ __device__ inline int stream_kmax(const ModelDims& d) {
 
 __host__ __device__ inline size_t stream_attn_bytes(const ModelDims& d) {
   int G = d.hq / d.hkv;
-  return ((size_t)(G + 2) * d.hd + (size_t)G * (kStreamMaxStagedRows + 1) + 4 * G) * 4;
+  return ((size_t)(G + 2) * d.hd + (size_t)G * (kStreamMaxStagedRows + 1) + 4 * G) * 4;   // q, k, v, scores
 }
 
 __host__ __device__ inline size_t stream_fixed_bytes(const ModelDims& d, int ncols) {
@@ -159,7 +159,8 @@ __host__ inline bool stream_model_fits(const ModelDims& d, int o_slices, int dow
   if (d.d / 4 > kMaxV4 * kDecThreads) return false;
   if (d.hq / d.hkv * d.hd > 2 * kDecThreads) return false;
   int esz = d.kv_dtype == 0 ? 4 : 2;
-  return half_bytes >= 2 * d.hd * esz + d.hd * 4 + 64;   // at least one staged K/V row pair + RoPE row
+  if (half_bytes < (int)((size_t)kDecThreads * (d.hq / d.hkv) * 4 + 1024)) return false;   // key-part reduction of the attention
+  return half_bytes >= 2 * d.hd * esz + 3 * d.hd * 4 + 64;   // at least one staged K/V row pair + RoPE row + gains
 }
 
 __device__ __noinline__ void stream_make_plans(const DecodeArgs& a, StreamCtx& c, int cta, int ncta) {
@@ -202,7 +203,7 @@ __device__ __noinline__ void stream_producer(const DecodeArgs& a, StreamCtx& c, 
     FillDesc d;
     d.ph = cur.ph; d.layer = cur.layer; d.round = cur.round; d.valid = 0;
     d.ta = d.ntile = d.ktn = d.has_gains = 0;
-    d.col = d.kvh = d.split = d.nsplit = d.k0 = d.npre = d.is_global = d.pad = 0;
+    d.col = d.kvh = d.split = d.nsplit = d.k0 = d.npre = d.is_global = d.pos = 0;
     if (cur.ph == kSB) {
       // token / position of this step must be final before its rows are chosen
       for (long spins = 0; *c.step_ready <= cur.step; ++spins) {
@@ -219,10 +220,14 @@ __device__ __noinline__ void stream_producer(const DecodeArgs& a, StreamCtx& c, 
         d.kvh = rest % dm.hkv;
         d.col = rest / dm.hkv;
         int pos = __ldcg(&a.st->pos[d.col]);
-        if (pos < 0 || pos >= dm.max_ctx) pos = 0;
+        if (pos < 0 || pos >= dm.max_ctx) {
+          if (lane == 0) atomicExch(&a.st->err, (int)kDevBadPosition);
+          pos = 0;
+        }
         int k0, k1;
         attn_split_range(dm, pos, d.is_global, d.nsplit, d.split, &k0, &k1);
         d.k0 = k0;
+        d.pos = pos;
         int nold = min(k1, pos) - k0;        // the row of `pos` itself is not in the cache yet
         d.npre = nold < 0 ? 0 : min(nold, c.npre_max);
         if (lane == 0) c.slot[h] = d;
@@ -230,7 +235,8 @@ __device__ __noinline__ void stream_producer(const DecodeArgs& a, StreamCtx& c, 
         const int esz = dm.kv_dtype == 0 ? 4 : 2;
         const uint32_t row = (uint32_t)dm.hd * esz;
         const uint32_t rope_row = (uint32_t)(dm.hd / 2) * 4;
-        if (lane == 0) mbar_arrive_expect_tx(bar, 2u * d.npre * row + 2u * rope_row);
+        const uint32_t gain_row = (uint32_t)dm.hd * 4;
+        if (lane == 0) mbar_arrive_expect_tx(bar, 2u * d.npre * row + 2u * rope_row + 2u * gain_row);
         __syncwarp();
         const int* ptab = a.page_table + (size_t)d.col * a.pages_per_seq;
         const unsigned char* kb = reinterpret_cast<const unsigned char*>(c.lkv[cur.layer].k);
@@ -245,6 +251,11 @@ __device__ __noinline__ void stream_producer(const DecodeArgs& a, StreamCtx& c, 
           unsigned char* rp = dst + (size_t)2 * c.npre_max * row;
           bulk_load_1d(rp, a.rope_cos[t] + (size_t)pos * (dm.hd / 2), rope_row, bar);
           bulk_load_1d(rp + rope_row, a.rope_sin[t] + (size_t)pos * (dm.hd / 2), rope_row, bar);
+        }
+        if (lane == 30) {     // QK-norm gains behind the RoPE rows
+          unsigned char* gp = dst + (size_t)2 * c.npre_max * row + 2u * rope_row;
+          bulk_load_1d(gp, c.lw[cur.layer].g_q, gain_row, bar);
+          bulk_load_1d(gp + gain_row, c.lw[cur.layer].g_k, gain_row, bar);
         }
       }
     } else {
@@ -513,10 +524,30 @@ __device__ __forceinline__ float4 load4_smem(const T* p) {
   }
 }
 
+// This lane's DPL elements of a row of HD = 32 * DPL values: a staged K row (cache type T), or an fp32
+// row in shared memory when `row` is null.  For DPL >= 4 the lane takes 4-element groups 128 elements
+// apart (group c = elements c*128 + 4*lane ..), so a warp's 16-byte loads fall on consecutive addresses.
+template <typename T, int DPL>
+__device__ __forceinline__ void stream_load_dims(const T* row, const float* fresh, int lane, float (&out)[DPL]) {
+  if constexpr (DPL % 4 == 0) {
+#pragma unroll
+    for (int c = 0; c < DPL / 4; ++c) {
+      float4 t = row ? load4_smem<T>(row + c * 128 + 4 * lane) : *reinterpret_cast<const float4*>(fresh + c * 128 + 4 * lane);
+      out[4 * c] = t.x; out[4 * c + 1] = t.y; out[4 * c + 2] = t.z; out[4 * c + 3] = t.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < DPL; ++i) out[i] = row ? kv_to_float<T>(row[lane * DPL + i]) : fresh[lane * DPL + i];
+  }
+}
+
 struct AttnItem {
   int layer, col, kvh, split, nsplit, is_global;
+  int bar;                  // barrier index of the phase (timeline stamps)
+  int pos;                  // position of the query
   int nstaged;              // rows of chunk 0 already in the half (prefetched), else -1
   const float *cos_r, *sin_r;   // RoPE row of the query position (shared or global memory)
+  const float *g_q, *g_k;       // QK-norm gains (shared or global memory)
 };
 
 template <typename T, int HD, int G>
@@ -525,29 +556,29 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   constexpr int half = HD / 2, C4 = HD / 4;
   const int qi = it.col, kvh = it.kvh;
+  const int bar = it.bar;
   const LayerWeights& L = c.lw[it.layer];
   const LayerKv kv = c.lkv[it.layer];
-  int pos = __ldcg(&a.st->pos[qi]);
-  if (pos < 0 || pos >= dm.max_ctx) {
-    if (threadIdx.x == 0) atomicExch(&a.st->err, (int)kDevBadPosition);
-    pos = 0;
-  }
+  const int pos = it.pos;
   const int cap = c.npre_max;
   float* q_s = c.s.attn;               // [G][HD]
   float* k_s = q_s + G * HD;           // [HD] new key (normed, roped)
   float* v_s = k_s + HD;               // [HD]
-  float* sc = v_s + HD;                // [G][cap + 1] scores, then probabilities
-  float* st = sc + G * (cap + 1);      // [G][4]: m, l, corr
+  float* sc = v_s + HD;                // [G][cap + 1] probabilities exp(score - bound)
   const size_t rowb = (size_t)HD * sizeof(T);
   const T* kpre = reinterpret_cast<const T*>(hb);
   const T* vpre = reinterpret_cast<const T*>(hb + (size_t)cap * rowb);
   const float* row = a.qkv + (size_t)qi * dm.nqkv();
   const float att_scale = rsqrtf((float)HD);
+  // Q and K are RMS-normalised, so every score is at most L.attn_bound in magnitude: the softmax is
+  // shifted by that constant instead of a running maximum, and the partial sums of the splits
+  // simply add up (no per-split maximum, no rescaling).
+  const float shift = L.attn_bound;
   // ---- stage q heads, the new key and value
   for (int h = warp; h < G + 2; h += kDecWarps) {
     if (h <= G) {
       const float* src = h < G ? row + (size_t)(kvh * G + h) * HD : row + dm.nq() + (size_t)kvh * HD;
-      const float* gain = h < G ? L.g_q : L.g_k;
+      const float* gain = h < G ? it.g_q : it.g_k;
       float* dst = h < G ? q_s + h * HD : k_s;
       float v[HD / 32];
       float ss = 0.f;
@@ -580,8 +611,8 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
       for (int i = 0; i < HD / 32; ++i) v_s[lane + 32 * i] = __ldcg(src + lane + 32 * i);
     }
   }
-  if (threadIdx.x < G) { st[threadIdx.x * 4] = -INFINITY; st[threadIdx.x * 4 + 1] = 0.f; st[threadIdx.x * 4 + 2] = 1.f; }
   dec_sync();
+  B2_TP(2);
   const int* ptab = a.page_table + (size_t)qi * a.pages_per_seq;
   if (it.split == 0) {     // KV append: exactly one CTA per (query, kv head)
     T* kbase = reinterpret_cast<T*>(kv.k);
@@ -599,6 +630,7 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
       }
       if (kv.v16) kv.v16[(((size_t)page * dm.hkv + kvh) * HD + e) * kPage + slot] = __float2bfloat16(v_s[e]);
     }
+    asm volatile("fence.proxy.async.global;" ::: "memory");   // later steps fetch these rows with bulk async copies
   }
   int k0, k1;
   attn_split_range(dm, pos, it.is_global, it.nsplit, it.split, &k0, &k1);
@@ -611,7 +643,17 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
     }
     dec_sync();
   }
-  float o0 = 0.f, o1 = 0.f;     // outputs idx = threadIdx.x and threadIdx.x + kDecThreads of [G][HD]
+  // P.V ownership: thread = (element e of the head dimension, key part kp); it accumulates all G heads
+  constexpr int KP = kDecThreads / HD;               // key parts
+  constexpr int DPL = HD / 32;                       // dims of a row per lane in the score stage
+  const int pv_e = threadIdx.x % HD, pv_part = threadIdx.x / HD;
+  float o[G], lsum[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) { o[g] = 0.f; lsum[g] = 0.f; }
+  // the score stage keeps this lane's dims of every q head in registers
+  float qreg[G][DPL];
+#pragma unroll
+  for (int g = 0; g < G; ++g) stream_load_dims<float, DPL>(nullptr, q_s + g * HD, lane, qreg[g]);
   const int nchunks = n_old <= 0 ? 1 : (n_old + cap - 1) / cap;
   for (int ch = 0; ch < nchunks; ++ch) {
     const int c0 = ch * cap;
@@ -636,138 +678,141 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
     }
     const bool lastc = ch == nchunks - 1;
     const int nk = nrows + ((lastc && has_new) ? 1 : 0);
-    // ---- scores
-    for (int p = threadIdx.x; p < G * nk; p += kDecThreads) {
-      const int g = p / nk, kk = p - g * nk;
-      const float* qrow = q_s + g * HD;
-      float acc = 0.f;
-      if (kk < nrows) {
-        const T* kr = kpre + (size_t)kk * HD;
-#pragma unroll 4
-        for (int i = 0; i < C4; ++i) {
-          const int cc = (i + lane) & (C4 - 1);
-          float4 kx = load4_smem<T>(kr + 4 * cc);
-          float4 qv = *reinterpret_cast<const float4*>(qrow + 4 * cc);
-          acc += kx.x * qv.x + kx.y * qv.y + kx.z * qv.z + kx.w * qv.w;
-        }
+    if (ch == 0) B2_TP(7);
+    // ---- probabilities p[key][head] = exp(q_head . k_key - shift): a warp takes two keys at a time,
+    //      lane l the dims [l*DPL, (l+1)*DPL) of both rows against all G heads; each K row is read once
+    for (int kp = warp; 2 * kp < nk; kp += kDecWarps) {
+      const int ka = 2 * kp, kb_ = min(2 * kp + 1, nk - 1);
+      float xa[DPL], xb[DPL];
+      stream_load_dims<T, DPL>(ka < nrows ? kpre + (size_t)ka * HD : nullptr, k_s, lane, xa);
+      stream_load_dims<T, DPL>(kb_ < nrows ? kpre + (size_t)kb_ * HD : nullptr, k_s, lane, xb);
+      float acc[2 * G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int i = 0; i < DPL; ++i) { sa += qreg[g][i] * xa[i]; sb += qreg[g][i] * xb[i]; }
+        acc[2 * g] = sa;
+        acc[2 * g + 1] = sb;
+      }
+#pragma unroll
+      for (int j = 0; j < 2 * G; ++j) acc[j] = warp_sum(acc[j]);
+      if (lane < 2 * G) {
+        const int g = lane >> 1, second = lane & 1;
+        float v = acc[0];
+#pragma unroll
+        for (int j = 1; j < 2 * G; ++j) v = lane == j ? acc[j] : v;
+        const int kk = second ? 2 * kp + 1 : ka;
+        if (kk < nk) sc[kk * G + g] = __expf(v - shift);
+      }
+    }
+    dec_sync();
+    if (ch == 0) B2_TP(3);
+    // ---- P.V and the row sums: this thread's element of V against the probabilities of all heads
+    for (int kk = pv_part; kk < nk; kk += KP) {
+      const float v = kk < nrows ? kv_to_float<T>(vpre[(size_t)kk * HD + pv_e]) : v_s[pv_e];
+      float pg[G];
+      if constexpr (G == 4) {          // one 16-byte broadcast load for the four heads
+        const float4 t = *reinterpret_cast<const float4*>(sc + kk * 4);
+        pg[0] = t.x; pg[1] = t.y; pg[2] = t.z; pg[3] = t.w;
       } else {
-#pragma unroll 4
-        for (int i = 0; i < C4; ++i) {
-          const int cc = (i + lane) & (C4 - 1);
-          float4 kx = *reinterpret_cast<const float4*>(k_s + 4 * cc);
-          float4 qv = *reinterpret_cast<const float4*>(qrow + 4 * cc);
-          acc += kx.x * qv.x + kx.y * qv.y + kx.z * qv.z + kx.w * qv.w;
-        }
-      }
-      sc[g * (cap + 1) + kk] = acc;
-    }
-    dec_sync();
-    // ---- softmax statistics of this chunk, merged into the running (m, l)
-    if (warp < G) {
-      float* sg = sc + warp * (cap + 1);
-      float mc = -INFINITY;
-      for (int kk = lane; kk < nk; kk += 32) mc = fmaxf(mc, sg[kk]);
-      mc = warp_max(mc);
-      const float m_old = st[warp * 4], l_old = st[warp * 4 + 1];
-      const float m_new = fmaxf(m_old, mc);
-      float lc = 0.f;
-      for (int kk = lane; kk < nk; kk += 32) {
-        float pv = __expf(sg[kk] - m_new);
-        sg[kk] = pv;
-        lc += pv;
-      }
-      lc = warp_sum(lc);
-      if (lane == 0) {
-        const float corr = m_new == -INFINITY ? 1.0f : __expf(m_old - m_new);
-        st[warp * 4] = m_new;
-        st[warp * 4 + 1] = l_old * corr + lc;
-        st[warp * 4 + 2] = corr;
-      }
-    }
-    dec_sync();
-    // ---- P.V for the outputs this thread owns
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
-      const int idx = threadIdx.x + u * kDecThreads;
-      if (idx < G * HD) {
-        const int g = idx / HD, e = idx - g * HD;
-        const float* sg = sc + g * (cap + 1);
-        float acc = (u == 0 ? o0 : o1) * st[g * 4 + 2];
-        int kk = 0;
-        for (; kk + 4 <= nrows; kk += 4) {
-          float v0 = kv_to_float<T>(vpre[(size_t)kk * HD + e]), v1 = kv_to_float<T>(vpre[(size_t)(kk + 1) * HD + e]);
-          float v2 = kv_to_float<T>(vpre[(size_t)(kk + 2) * HD + e]), v3 = kv_to_float<T>(vpre[(size_t)(kk + 3) * HD + e]);
-          acc += sg[kk] * v0 + sg[kk + 1] * v1 + sg[kk + 2] * v2 + sg[kk + 3] * v3;
-        }
-        for (; kk < nrows; ++kk) acc += sg[kk] * kv_to_float<T>(vpre[(size_t)kk * HD + e]);
-        if (nk > nrows) acc += sg[nrows] * v_s[e];
-        if (u == 0) o0 = acc; else o1 = acc;
+        for (int g = 0; g < G; ++g) pg[g] = sc[kk * G + g];
+      }
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        o[g] += pg[g] * v;
+        lsum[g] += pg[g];
       }
     }
+    if (ch + 1 < nchunks) dec_sync();      // the next chunk overwrites the rows and the probabilities
   }
-  // ---- partial result of this split: (m, l, unnormalised o)
-  static_assert(G * HD <= 2 * kDecThreads, "two outputs per thread cover the group");
+  B2_TP(5);
+  // ---- the key parts meet in shared memory (over the K rows, which are not needed any more),
+  //      then part 0 writes the split's partial result: row sum l and unnormalised o, both relative to the shift
+  dec_sync();
+  float* ored = reinterpret_cast<float*>(hb);                  // [KP][G][HD]
+  float* lred = ored + (size_t)KP * G * HD;                    // [KP][G]
+  if (pv_part > 0) {
 #pragma unroll
-  for (int u = 0; u < 2; ++u) {
-    const int idx = threadIdx.x + u * kDecThreads;
-    if (idx < G * HD) {
-      const int g = idx / HD, e = idx - g * HD;
+    for (int g = 0; g < G; ++g) ored[((size_t)pv_part * G + g) * HD + pv_e] = o[g];
+  }
+  if (pv_e == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) lred[pv_part * G + g] = lsum[g];
+  }
+  dec_sync();
+  if (pv_part == 0) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float acc = o[g];
+      for (int kp = 1; kp < KP; ++kp) acc += ored[((size_t)kp * G + g) * HD + pv_e];
       size_t pi = (((size_t)qi * dm.hkv + kvh) * it.nsplit + it.split) * G + g;
-      a.part_o[pi * HD + e] = u == 0 ? o0 : o1;
-      if (e == 0) { a.part_ml[pi * 2] = st[g * 4]; a.part_ml[pi * 2 + 1] = st[g * 4 + 1]; }
+      a.part_o[pi * HD + pv_e] = acc;
+      if (pv_e == 0) {
+        float ls = 0.f;
+        for (int kp = 0; kp < KP; ++kp) ls += lred[kp * G + g];
+        a.part_ml[pi * 2] = shift;
+        a.part_ml[pi * 2 + 1] = ls;
+      }
     }
   }
   dec_sync();
+  B2_TP(6);
 }
 
-// Log-sum-exp combine of the split partials of one head slice into xf (then quantised).
-// All loads of a thread are independent, so they overlap.
+// Combine of the split partials of one head slice into xf (then quantised).  All splits share one
+// softmax shift, so the combine is sum(o) / sum(l).  The splits of an output are dealt to as many
+// threads as the block has per output, every load of a thread is independent of the others, and
+// the per-thread sums meet in shared memory.
 __device__ __forceinline__ void stream_prologue_combine(const DecodeArgs& a, StreamCtx& c, int layer) {
   const ModelDims& dm = a.dims;
   const PhasePlan& p = c.plan[kSC];
   const int Ks = dm.nq() / a.o_slices, hps = Ks / dm.hd, G = dm.group();
   const int nsplit = c.lw[layer].is_global ? a.n_attn_splits_global : a.n_attn_splits_local;
-  float* mls = c.s.argbuf;                       // [hps][nsplit][2]
-  float* wts = c.s.argbuf + kDecThreads;         // [hps][nsplit] normalised weights
+  int tpo = 1;                                    // threads per output: a power of two
+  while (tpo * 2 * Ks <= kDecThreads && tpo * 2 <= nsplit && tpo < 8) tpo *= 2;
+  float* part = c.s.argbuf;                       // [tpo][Ks][2] partial (o, l): tpo * Ks <= kDecThreads, argbuf holds 2 * kDecThreads
   for (int col = 0; col < a.ncols; ++col) {
     if (col > 0) dec_sync();
-    for (int i = threadIdx.x; i < hps * nsplit * 2; i += kDecThreads) {
-      int hh = i / (nsplit * 2), rem = i - hh * nsplit * 2, sp = rem >> 1, w = rem & 1;
-      int h = p.slice * hps + hh, kvh = h / G, g = h % G;
-      size_t pi = (((size_t)col * dm.hkv + kvh) * nsplit + sp) * G + g;
-      mls[i] = __ldcg(a.part_ml + pi * 2 + w);
-    }
-    dec_sync();
-    for (int hh = threadIdx.x >> 5; hh < hps; hh += kDecWarps) {
-      const int lane = threadIdx.x & 31;
-      const float* ml = mls + (size_t)hh * nsplit * 2;
-      float M = -INFINITY;
-      for (int sp = lane; sp < nsplit; sp += 32) M = fmaxf(M, ml[sp * 2]);
-      M = warp_max(M);
-      float Lsum = 0.f;
-      for (int sp = lane; sp < nsplit; sp += 32) Lsum += ml[sp * 2 + 1] * __expf(ml[sp * 2] - M);
-      Lsum = warp_sum(Lsum);
-      const float invL = Lsum > 0.f ? 1.0f / Lsum : 0.f;
-      for (int sp = lane; sp < nsplit; sp += 32) wts[hh * nsplit + sp] = __expf(ml[sp * 2] - M) * invL;
-    }
-    dec_sync();
-    for (int i = threadIdx.x; i < Ks; i += kDecThreads) {
+    const int i = threadIdx.x % Ks, part_id = threadIdx.x / Ks;
+    if (part_id < tpo && Ks <= kDecThreads) {
       int hh = i / dm.hd, e = i - hh * dm.hd;
       int h = p.slice * hps + hh, kvh = h / G, g = h % G;
-      const float* po = a.part_o + ((((size_t)col * dm.hkv + kvh) * nsplit) * G + g) * dm.hd + e;
-      const size_t stride = (size_t)G * dm.hd;
-      const float* w = wts + hh * nsplit;
-      float acc = 0.f;
-      int sp = 0;
-      for (; sp + 16 <= nsplit; sp += 16) {
-        float v[16];
+      const size_t pi0 = (((size_t)col * dm.hkv + kvh) * nsplit) * G + g;
+      const float* po = a.part_o + pi0 * dm.hd + e;
+      const float* pl = a.part_ml + pi0 * 2 + 1;
+      const size_t stride = (size_t)G * dm.hd, lstride = (size_t)G * 2;
+      const int per = (nsplit + tpo - 1) / tpo;
+      const int s0 = part_id * per, s1 = min(nsplit, s0 + per);
+      float acc = 0.f, ls = 0.f;
+      int sp = s0;
+      for (; sp + 8 <= s1; sp += 8) {
+        float v[8], w[8];
 #pragma unroll
-        for (int u = 0; u < 16; ++u) v[u] = __ldcg(po + (size_t)(sp + u) * stride);
+        for (int u = 0; u < 8; ++u) { v[u] = __ldcg(po + (size_t)(sp + u) * stride); w[u] = __ldcg(pl + (size_t)(sp + u) * lstride); }
 #pragma unroll
-        for (int u = 0; u < 16; ++u) acc += v[u] * w[sp + u];
+        for (int u = 0; u < 8; ++u) { acc += v[u]; ls += w[u]; }
       }
-      for (; sp < nsplit; ++sp) acc += __ldcg(po + (size_t)sp * stride) * w[sp];
-      c.s.xf[(size_t)col * Ks + i] = acc;
+      for (; sp < s1; ++sp) { acc += __ldcg(po + (size_t)sp * stride); ls += __ldcg(pl + (size_t)sp * lstride); }
+      part[((size_t)part_id * Ks + i) * 2] = acc;
+      part[((size_t)part_id * Ks + i) * 2 + 1] = ls;
+    }
+    dec_sync();
+    for (int j = threadIdx.x; j < Ks; j += kDecThreads) {
+      float acc = 0.f, ls = 0.f;
+      if (Ks <= kDecThreads) {
+        for (int t = 0; t < tpo; ++t) { acc += part[((size_t)t * Ks + j) * 2]; ls += part[((size_t)t * Ks + j) * 2 + 1]; }
+      } else {                                     // wide slices: one thread walks all splits of an output
+        int hh = j / dm.hd, e = j - hh * dm.hd;
+        int h = p.slice * hps + hh, kvh = h / G, g = h % G;
+        const size_t pi0 = (((size_t)col * dm.hkv + kvh) * nsplit) * G + g;
+        for (int sp = 0; sp < nsplit; ++sp) {
+          acc += __ldcg(a.part_o + (pi0 + (size_t)sp * G) * dm.hd + e);
+          ls += __ldcg(a.part_ml + (pi0 + (size_t)sp * G) * 2 + 1);
+        }
+      }
+      c.s.xf[(size_t)col * Ks + j] = ls > 0.f ? acc / ls : 0.f;
     }
   }
   dec_sync();
@@ -884,7 +929,7 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
   }
   for (int i = threadIdx.x; i < kMaxRoundUnits * 16 * kQCols; i += kStreamThreads) c.s.red[i] = 0;
   constexpr int esz_kv = (int)sizeof(T);
-  c.npre_max = min(kStreamMaxStagedRows, (half_bytes - HD * 4) / (2 * HD * esz_kv));
+  c.npre_max = min(kStreamMaxStagedRows, (half_bytes - 3 * HD * 4) / (2 * HD * esz_kv));
   c.wait_no = 0;
   c.aux_cnt = 0;
   __syncthreads();
@@ -931,19 +976,34 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
           it.col = rest / dm.hkv;
           it.nsplit = nsplit;
           it.is_global = is_global;
+          it.bar = bar;
           if (itx == cta && fd->valid && fd->ph == kSB) {
             it.nstaged = fd->npre;
+            it.pos = fd->pos;
             it.cos_r = reinterpret_cast<const float*>(hb + (size_t)2 * c.npre_max * rowb);
             it.sin_r = it.cos_r + HD / 2;
+            it.g_q = it.sin_r + HD / 2;
+            it.g_k = it.g_q + HD;
           } else {            // further items of this CTA: rows fetched on the spot
             int pos = __ldcg(&a.st->pos[it.col]);
-            if (pos < 0 || pos >= dm.max_ctx) pos = 0;
+            if (pos < 0 || pos >= dm.max_ctx) {
+              if (threadIdx.x == 0) atomicExch(&a.st->err, (int)kDevBadPosition);
+              pos = 0;
+            }
+            it.pos = pos;
             it.nstaged = -1;
             it.cos_r = a.rope_cos[is_global ? 1 : 0] + (size_t)pos * (HD / 2);
             it.sin_r = a.rope_sin[is_global ? 1 : 0] + (size_t)pos * (HD / 2);
+            it.g_q = L.g_q;
+            it.g_k = L.g_k;
           }
 #ifndef B2_SZ_NO_ATTN
+#ifdef B2_DBG_ATTN_TWICE
+#pragma unroll 1
+          for (int rep = 0; rep < 2; ++rep) attn_smem_item<T, HD, G>(a, c, it, hb);   // timeline shows the second, warm run
+#else
           attn_smem_item<T, HD, G>(a, c, it, hb);
+#endif
 #endif
         }
         B2_TP(4);

@@ -158,6 +158,7 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
       float mq = 0.f, mk = 0.f;
       for (int k = 0; k < d.hd; ++k) { mq = std::max(mq, std::fabs(gq[k])); mk = std::max(mk, std::fabs(gk[k])); }
       m->attn_bound.push_back(std::sqrt((float)d.hd) * mq * mk * 1.01f);
+      L.attn_bound = m->attn_bound.back();
     }
     L.g_q = fvec(p + "q_norm", d.hd);
     L.g_k = fvec(p + "k_norm", d.hd);
@@ -448,6 +449,7 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
     long room = ((long)prop.sharedMemPerBlockOptin - (long)fixed - 2048) / 2;   // margin: static shared memory
     int half = (int)std::min<long>(room, 96 * 1024) / 1024 * 1024;
     bool ok = half > 0 && stream_model_fits(d, a.o_slices, a.down_slices, half) && prop.cooperativeLaunch;
+    for (float b : model->attn_bound) ok = ok && b <= kFaMaxBound;   // its attention shifts the softmax by the bound
     if (ok) {
       e->stream_half = half;
       e->stream_smem = fixed + 2 * (size_t)half;

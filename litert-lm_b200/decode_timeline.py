@@ -90,7 +90,9 @@ def main() -> None:
                 ok = (p[:, :, lo] > 0) & (p[:, :, hi] > 0)
                 d = np.where(ok, (p[:, :, hi] - p[:, :, lo]) * us, np.nan)
                 seg.append((labels[k], float(np.nanmean(d)) if ok.any() else float("nan")))
-            for lo, hi, nm in ((1, 2, "loads+sums"), (2, 7, "block reduce"), (7, 3, "quantize")):
+            inner = (((1, 2, "stage q/k/v"), (2, 7, "append + ranges"), (7, 3, "scores"), (3, 5, "P.V"), (5, 6, "reduce + write partials"))
+                     if cls == "attention" else ((1, 2, "loads+sums"), (2, 7, "block reduce"), (7, 3, "quantize")))
+            for lo, hi, nm in inner:
                 ok = (p[:, :, lo] > 0) & (p[:, :, hi] > 0)
                 if ok.any():
                     seg.append((nm, float(np.nanmean(np.where(ok, (p[:, :, hi] - p[:, :, lo]) * us, np.nan)))))
