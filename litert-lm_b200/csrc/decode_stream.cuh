@@ -763,59 +763,75 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
 
 // Combine of the split partials of one head slice into xf (then quantised).  All splits share one
 // softmax shift, so the combine is sum(o) / sum(l).  The splits of an output are dealt to as many
-// threads as the block has per output, every load of a thread is independent of the others, and
-// the per-thread sums meet in shared memory.
-__device__ __forceinline__ void stream_prologue_combine(const DecodeArgs& a, StreamCtx& c, int layer) {
+// threads as the block has per output and every load of a thread is independent of the others.
+// The row sums l are fetched by ONE warp per head of the slice (a lane per split): they are a few
+// cache lines that every CTA of the grid reads, so each CTA asks for them once, not once per thread.
+__device__ __forceinline__ void stream_prologue_combine(const DecodeArgs& a, StreamCtx& c, int layer, int bar) {
   const ModelDims& dm = a.dims;
   const PhasePlan& p = c.plan[kSC];
   const int Ks = dm.nq() / a.o_slices, hps = Ks / dm.hd, G = dm.group();
   const int nsplit = c.lw[layer].is_global ? a.n_attn_splits_global : a.n_attn_splits_local;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   int tpo = 1;                                    // threads per output: a power of two
   while (tpo * 2 * Ks <= kDecThreads && tpo * 2 <= nsplit && tpo < 8) tpo *= 2;
-  float* part = c.s.argbuf;                       // [tpo][Ks][2] partial (o, l): tpo * Ks <= kDecThreads, argbuf holds 2 * kDecThreads
+  float* part = c.s.argbuf;                       // [tpo][Ks] partial o: tpo * Ks <= kDecThreads
+  float* lsum = c.s.argbuf + kDecThreads;         // [hps] row sums over all splits (hps <= kDecThreads)
   for (int col = 0; col < a.ncols; ++col) {
     if (col > 0) dec_sync();
+    for (int hh = warp; hh < hps; hh += kDecWarps) {
+      int h = p.slice * hps + hh, kvh = h / G, g = h % G;
+      const float* pl = a.part_ml + ((((size_t)col * dm.hkv + kvh) * nsplit) * G + g) * 2 + 1;
+      float ls = 0.f;
+      for (int sp = lane; sp < nsplit; sp += 32) ls += __ldcg(pl + (size_t)sp * G * 2);
+      ls = warp_sum(ls);
+      if (lane == 0) lsum[hh] = ls;
+    }
     const int i = threadIdx.x % Ks, part_id = threadIdx.x / Ks;
     if (part_id < tpo && Ks <= kDecThreads) {
       int hh = i / dm.hd, e = i - hh * dm.hd;
       int h = p.slice * hps + hh, kvh = h / G, g = h % G;
       const size_t pi0 = (((size_t)col * dm.hkv + kvh) * nsplit) * G + g;
       const float* po = a.part_o + pi0 * dm.hd + e;
-      const float* pl = a.part_ml + pi0 * 2 + 1;
-      const size_t stride = (size_t)G * dm.hd, lstride = (size_t)G * 2;
+      const size_t stride = (size_t)G * dm.hd;
       const int per = (nsplit + tpo - 1) / tpo;
       const int s0 = part_id * per, s1 = min(nsplit, s0 + per);
-      float acc = 0.f, ls = 0.f;
+      float acc = 0.f;
       int sp = s0;
-      for (; sp + 8 <= s1; sp += 8) {
-        float v[8], w[8];
+      for (; sp + 16 <= s1; sp += 16) {
+        float v[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { v[u] = __ldcg(po + (size_t)(sp + u) * stride); w[u] = __ldcg(pl + (size_t)(sp + u) * lstride); }
+        for (int u = 0; u < 16; ++u) v[u] = __ldcg(po + (size_t)(sp + u) * stride);
 #pragma unroll
-        for (int u = 0; u < 8; ++u) { acc += v[u]; ls += w[u]; }
+        for (int u = 0; u < 16; ++u) acc += v[u];
       }
-      for (; sp < s1; ++sp) { acc += __ldcg(po + (size_t)sp * stride); ls += __ldcg(pl + (size_t)sp * lstride); }
-      part[((size_t)part_id * Ks + i) * 2] = acc;
-      part[((size_t)part_id * Ks + i) * 2 + 1] = ls;
+      for (; sp + 4 <= s1; sp += 4) {
+        float v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = __ldcg(po + (size_t)(sp + u) * stride);
+        acc += (v[0] + v[1]) + (v[2] + v[3]);
+      }
+      for (; sp < s1; ++sp) acc += __ldcg(po + (size_t)sp * stride);
+      part[(size_t)part_id * Ks + i] = acc;
     }
     dec_sync();
+    if (col == 0) B2_TP(2);
     for (int j = threadIdx.x; j < Ks; j += kDecThreads) {
-      float acc = 0.f, ls = 0.f;
+      const int hh = j / dm.hd;
+      float acc = 0.f;
       if (Ks <= kDecThreads) {
-        for (int t = 0; t < tpo; ++t) { acc += part[((size_t)t * Ks + j) * 2]; ls += part[((size_t)t * Ks + j) * 2 + 1]; }
+        for (int t = 0; t < tpo; ++t) acc += part[(size_t)t * Ks + j];
       } else {                                     // wide slices: one thread walks all splits of an output
-        int hh = j / dm.hd, e = j - hh * dm.hd;
+        int e = j - hh * dm.hd;
         int h = p.slice * hps + hh, kvh = h / G, g = h % G;
         const size_t pi0 = (((size_t)col * dm.hkv + kvh) * nsplit) * G + g;
-        for (int sp = 0; sp < nsplit; ++sp) {
-          acc += __ldcg(a.part_o + (pi0 + (size_t)sp * G) * dm.hd + e);
-          ls += __ldcg(a.part_ml + (pi0 + (size_t)sp * G) * 2 + 1);
-        }
+        for (int sp = 0; sp < nsplit; ++sp) acc += __ldcg(a.part_o + (pi0 + (size_t)sp * G) * dm.hd + e);
       }
+      const float ls = lsum[hh];
       c.s.xf[(size_t)col * Ks + j] = ls > 0.f ? acc / ls : 0.f;
     }
   }
   dec_sync();
+  B2_TP(7);
   quantize_cols(c.s, Ks, a.ncols, a.nterms);
 }
 
@@ -845,7 +861,7 @@ __device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx
         if (ph == kSA && layer == 0) {
           stream_prologue_embed(a, c, cta, a.xres[1], g_pre, L.gmax_pre_attn);
         } else if (ph == kSC) {
-          stream_prologue_combine(a, c, layer);
+          stream_prologue_combine(a, c, layer, bar);
         } else if (ph == kSE) {
           const int Ks = dm.ffn / a.down_slices;
           for (int col = 0; col < a.ncols; ++col)
