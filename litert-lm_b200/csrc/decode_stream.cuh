@@ -953,9 +953,7 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
   __syncthreads();
 
   if (threadIdx.x >= kDecThreads) {       // ---- producer warp
-#ifndef B2_SZ_NO_PRODUCER
     stream_producer(a, c, cta, nsteps);
-#endif
     return;
   }
 
@@ -1013,21 +1011,12 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
             it.g_q = L.g_q;
             it.g_k = L.g_k;
           }
-#ifndef B2_SZ_NO_ATTN
-#ifdef B2_DBG_ATTN_TWICE
-#pragma unroll 1
-          for (int rep = 0; rep < 2; ++rep) attn_smem_item<T, HD, G>(a, c, it, hb);   // timeline shows the second, warm run
-#else
           attn_smem_item<T, HD, G>(a, c, it, hb);
-#endif
-#endif
         }
         B2_TP(4);
         stream_release(c);
       } else {
-#ifndef B2_SZ_NO_GEMV
         stream_gemv_phase(a, c, ph, layer, cta, bv, bi, bar);
-#endif
       }
       if (ph == kSH) {       // CTA-level arg-max (lowest index wins ties), one slot per CTA
         float* sv = c.s.argbuf;
