@@ -243,15 +243,17 @@ __host__ __device__ inline size_t dec_attn_floats(const ModelDims& d) {
   int G = d.hq / d.hkv;
   return (size_t)(G + 2) * d.hd + (size_t)kDecWarps * G * (d.hd + 2);
 }
+// rows of the quantised staging: three int8 terms per session, at most one MMA n-tile
+__host__ __device__ inline int dec_xq_rows(int ncols) { return ncols * 3 < kQCols ? ncols * 3 : kQCols; }
 __host__ __device__ inline size_t dec_smem_bytes(const ModelDims& d, int ncols) {
   int kmax = d.ffn > d.d ? d.ffn : d.d;
   if (d.hq * d.hd > kmax) kmax = d.hq * d.hd;
   size_t b = (size_t)ncols * kmax * 4;
-  b += (size_t)kQCols * dec_xstride(kmax);
+  b += (size_t)dec_xq_rows(ncols) * dec_xstride(kmax);
   b += (size_t)kMaxRoundUnits * 16 * kQCols * 4;
   b += 64 * 4 + kMaxCols * 4 + kQCols * 4 + 2 * kDecThreads * 4;
   b += dec_attn_floats(d) * 4;
-  return b + 256;
+  return b + 256 + 16;
 }
 __device__ inline DecodeSmem carve_smem(unsigned char* base, const ModelDims& d, int ncols) {
   int kmax = d.ffn > d.d ? d.ffn : d.d;
@@ -262,7 +264,8 @@ __device__ inline DecodeSmem carve_smem(unsigned char* base, const ModelDims& d,
   off += (size_t)ncols * kmax * 4;
   s.xstride = dec_xstride(kmax);
   s.xq = reinterpret_cast<int8_t*>(base + off);
-  off += (size_t)kQCols * s.xstride;
+  off += (size_t)dec_xq_rows(ncols) * s.xstride;
+  off = (off + 15) & ~size_t(15);
   s.red = reinterpret_cast<int*>(base + off);
   off += (size_t)kMaxRoundUnits * 16 * kQCols * 4;
   s.scratch = reinterpret_cast<float*>(base + off);

@@ -143,8 +143,26 @@ def config_gemma3_27b(seed: int = 4) -> ModelConfig:
                        buckets=(2048, 512, 128), seed=seed)
 
 
+def config_gemma3_4b_slice(seed: int = 3) -> ModelConfig:
+    """The 4B shape's layer geometry (hidden 2560, 8 query / 4 kv heads of 256, ffn 10240, window 1024)
+    on 6 layers (one global) and a 16 k vocabulary: every per-layer kernel shape of the full model, small
+    enough for the CPU oracle and a quick build."""
+    return ModelConfig("gemma3-4b-slice", n_layers=6, d_model=2560, n_q_heads=8, n_kv_heads=4,
+                       head_dim=256, ffn=10240, vocab=16384, max_ctx=2048, window=1024,
+                       buckets=(1024, 256, 64), seed=seed)
+
+
+def config_gemma3_27b_slice(seed: int = 4) -> ModelConfig:
+    """The 27B shape's layer geometry (hidden 5376, 32 query / 16 kv heads of 128, ffn 21504, window
+    1024) on 2 layers (one local, one global) and a 16 k vocabulary, one GPU (no tensor parallelism)."""
+    return ModelConfig("gemma3-27b-slice", n_layers=2, d_model=5376, n_q_heads=32, n_kv_heads=16,
+                       head_dim=128, ffn=21504, vocab=16384, max_ctx=2048, window=1024, global_period=2,
+                       buckets=(2048, 512, 128), seed=seed)
+
+
 CONFIGS = {"tiny": config_tiny, "small": config_small, "small-gqa": config_small_gqa, "gemma3-1b": config_gemma3_1b,
-           "gemma3-4b": config_gemma3_4b, "gemma3-27b": config_gemma3_27b}
+           "gemma3-4b": config_gemma3_4b, "gemma3-27b": config_gemma3_27b,
+           "gemma3-4b-slice": config_gemma3_4b_slice, "gemma3-27b-slice": config_gemma3_27b_slice}
 
 
 # --------------------------------------------------------------------------- int4
