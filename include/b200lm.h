@@ -83,7 +83,9 @@ int B200Lm_Prefill(B200LmExecutor* e, const int32_t* ids, int32_t n_ids, int32_t
 /* Replaces DecodeLogits(inputs) and Decode(inputs, logits)
  * (llm_litert_compiled_model_executor.cc:300-534): runs one step on *id (or on
  * the pending id when id == NULL; none pending -> InvalidArgument "No id
- * available to be decoded.") and writes vocab floats to host_logits. */
+ * available to be decoded.") and writes vocab floats to host_logits, which may
+ * be pageable or page-locked host memory (a page-locked buffer receives the
+ * device-to-host copy directly). */
 int B200Lm_DecodeLogits(B200LmExecutor* e, const int32_t* id_or_null, float* host_logits, char** err);
 
 /* Replaces Decode(output_tokens) (llm_litert_compiled_model_executor.cc:278-298):

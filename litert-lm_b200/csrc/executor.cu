@@ -346,6 +346,8 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
     e->own_stream = true;
   }
   e->max_num_tokens = cfg.max_num_tokens > 0 ? std::min(cfg.max_num_tokens, d.max_ctx) : d.max_ctx;
+  B2_CHECK(cfg.prefill_gemm >= B200LM_GEMM_AUTO && cfg.prefill_gemm <= B200LM_GEMM_TCGEN05, kInvalidArgument,
+           "prefill_gemm must be B200LM_GEMM_AUTO, _CHECK or _TCGEN05");
   e->prefill_gemm = cfg.prefill_gemm == B200LM_GEMM_AUTO ? (model->has_tc ? B200LM_GEMM_TCGEN05 : B200LM_GEMM_CHECK)
                                                           : cfg.prefill_gemm;
   B2_CHECK(e->prefill_gemm != B200LM_GEMM_TCGEN05 || model->has_tc, kFailedPrecondition,
@@ -782,10 +784,14 @@ void Executor::decode_logits(const int* id_or_null, float* host_logits) {
   push_decode_state(&id, &current_step, 1);
   launch_decode_steps(1);
   const size_t nb = sizeof(float) * (size_t)model->dims.vocab;
-  B2_CUDA(cudaMemcpyAsync(pin_logits, dargs.logits, nb, cudaMemcpyDeviceToHost, stream));
+  // a page-locked destination takes the copy directly; pageable memory goes through the pinned staging
+  cudaPointerAttributes pa{};
+  const bool direct = cudaPointerGetAttributes(&pa, host_logits) == cudaSuccess && pa.type == cudaMemoryTypeHost;
+  if (!direct) cudaGetLastError();
+  B2_CUDA(cudaMemcpyAsync(direct ? host_logits : pin_logits, dargs.logits, nb, cudaMemcpyDeviceToHost, stream));
   d2h_bytes += nb;
   check_device_error("DecodeLogits");
-  memcpy(host_logits, pin_logits, nb);
+  if (!direct) memcpy(host_logits, pin_logits, nb);
   ++current_step;
 }
 
