@@ -761,6 +761,45 @@ __device__ __forceinline__ void attn_smem_item(const DecodeArgs& a, StreamCtx& c
   B2_TP(6);
 }
 
+// Input of the down projection: this CTA's K slice of the GeGLU activations, quantised per session
+// with its own maximum.  The values stay in registers between the maximum and the quantisation
+// (up to kMaxV4Down float4 per thread); wider slices go through the shared staging vector.
+constexpr int kMaxV4Down = 4;
+__device__ __forceinline__ void stream_prologue_down(const DecodeArgs& a, StreamCtx& c, int slice) {
+  const ModelDims& dm = a.dims;
+  const int Ks = dm.ffn / a.down_slices, n4 = Ks / 4;
+  if (n4 > kMaxV4Down * kDecThreads) {
+    for (int col = 0; col < a.ncols; ++col)
+      for (int i = threadIdx.x; i < n4; i += kDecThreads)
+        reinterpret_cast<float4*>(c.s.xf + (size_t)col * Ks)[i] =
+            __ldcg(reinterpret_cast<const float4*>(a.act + (size_t)col * dm.ffn + (size_t)slice * Ks) + i);
+    dec_sync();
+    quantize_cols(c.s, Ks, a.ncols, a.nterms);
+    return;
+  }
+  for (int col = 0; col < a.ncols; ++col) {
+    const float4* src = reinterpret_cast<const float4*>(a.act + (size_t)col * dm.ffn + (size_t)slice * Ks);
+    float4 v[kMaxV4Down];
+    float m = 0.f;
+#pragma unroll
+    for (int u = 0; u < kMaxV4Down; ++u) {
+      const int i = threadIdx.x + u * kDecThreads;
+      v[u] = i < n4 ? __ldcg(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+    }
+    m = block_max(m, c.s.scratch);
+    const float inv = m > 0.f ? 127.0f / m : 0.f;
+    int8_t* q0 = c.s.xq + (size_t)(col * a.nterms) * c.s.xstride;
+#pragma unroll
+    for (int u = 0; u < kMaxV4Down; ++u) {
+      const int i = threadIdx.x + u * kDecThreads;
+      if (i < n4) quantize4(make_float4(v[u].x * inv, v[u].y * inv, v[u].z * inv, v[u].w * inv), a.nterms, q0 + 4 * i, c.s.xstride);
+    }
+    if (threadIdx.x == 0) c.s.colscale[col] = m > 0.f ? m / 127.0f : 0.f;
+    dec_sync();               // scratch is reused by the next session's maximum; xq is complete
+  }
+}
+
 // Combine of the split partials of one head slice into xf (then quantised).  All splits share one
 // softmax shift, so the combine is sum(o) / sum(l).  The splits of an output are dealt to as many
 // threads as the block has per output and every load of a thread is independent of the others.
@@ -829,10 +868,20 @@ __device__ __forceinline__ void stream_prologue_combine(const DecodeArgs& a, Str
       const float ls = lsum[hh];
       c.s.xf[(size_t)col * Ks + j] = ls > 0.f ? acc / ls : 0.f;
     }
+    if (Ks <= kDecThreads) {
+      // one output per thread: its value is still at hand for the maximum and the quantisation
+      dec_sync();
+      const bool mine = (int)threadIdx.x < Ks;
+      const float val = mine ? c.s.xf[(size_t)col * Ks + threadIdx.x] : 0.f;
+      const float m = block_max(fabsf(val), c.s.scratch);
+      const float inv = m > 0.f ? 127.0f / m : 0.f;
+      if (mine) quantize_value(val * inv, a.nterms, c.s.xq + (size_t)(col * a.nterms) * c.s.xstride + threadIdx.x, c.s.xstride);
+      if (threadIdx.x == 0) c.s.colscale[col] = m > 0.f ? m / 127.0f : 0.f;
+    }
   }
   dec_sync();
   B2_TP(7);
-  quantize_cols(c.s, Ks, a.ncols, a.nterms);
+  if (Ks > kDecThreads) quantize_cols(c.s, Ks, a.ncols, a.nterms);
 }
 
 // One GEMV phase of the stream: for every round acquire / (prologue) / MMA / epilogue / release.
@@ -863,13 +912,7 @@ __device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx
         } else if (ph == kSC) {
           stream_prologue_combine(a, c, layer, bar);
         } else if (ph == kSE) {
-          const int Ks = dm.ffn / a.down_slices;
-          for (int col = 0; col < a.ncols; ++col)
-            for (int i = threadIdx.x; i < Ks / 4; i += kDecThreads)
-              reinterpret_cast<float4*>(c.s.xf + (size_t)col * Ks)[i] =
-                  __ldcg(reinterpret_cast<const float4*>(a.act + (size_t)col * dm.ffn + (size_t)p.slice * Ks) + i);
-          dec_sync();
-          quantize_cols(c.s, Ks, a.ncols, a.nterms);
+          stream_prologue_down(a, c, p.slice);
         } else {
           // A (layer > 0), D and H: residual update + two norms, one reduction
           const bool isD = ph == kSD;
