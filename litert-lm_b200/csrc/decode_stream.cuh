@@ -336,6 +336,42 @@ __device__ __forceinline__ void stream_release(StreamCtx& c) {
   dec_sync();
   if (threadIdx.x == 0) mbar_arrive(&c.empty[h]);
 }
+// The same, with the block barrier and the arrive left to the grid barrier that follows at once
+// (stream_grid_barrier): one block barrier less per phase.
+__device__ __forceinline__ uint64_t* stream_release_deferred(StreamCtx& c) {
+  const unsigned h = c.wait_no & 1u;
+  ++c.wait_no;
+  return &c.empty[h];
+}
+
+// grid_barrier (decode_ops.cuh) that first hands a staging half back to the producer: the block barrier
+// at its entry is the one that release needs.
+__device__ __forceinline__ void stream_grid_barrier(DecodeState* st, unsigned int* epoch, int ncta, uint64_t* release,
+                                                    long long* trace, int bar_idx) {
+  dec_sync();
+  if (threadIdx.x == 0) {
+    if (release) mbar_arrive(release);
+    *epoch += (unsigned)ncta;
+    if (trace) trace[((size_t)bar_idx * ncta + blockIdx.x) * 2] = clock64();
+    __threadfence();
+    atomicAdd(&st->barrier, 1u);
+    unsigned int target = *epoch;
+    long spins = 0;
+    while (true) {
+      unsigned int v;
+      asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(&st->barrier));
+      if ((int)(v - target) >= 0) break;
+      ++spins;
+      if ((spins & 255) == 0 && *reinterpret_cast<volatile int*>(&st->err) == (int)kDevBarrierTimeout) break;
+      if (spins > 4000000L) {   // ~ a second; never reached in a healthy run
+        atomicExch(&st->err, (int)kDevBarrierTimeout);
+        break;
+      }
+    }
+    if (trace) trace[((size_t)bar_idx * ncta + blockIdx.x) * 2 + 1] = clock64();
+  }
+  dec_sync();
+}
 
 // tiles in shared memory: tile u at wsm + u * ktn * 32 (uint4 units)
 __device__ __forceinline__ void gemv_tiles_smem(const uint4* wsm, int ktn, int nu, QuantCols xc, int* red) {
@@ -886,8 +922,9 @@ __device__ __forceinline__ void stream_prologue_combine(const DecodeArgs& a, Str
 
 // One GEMV phase of the stream: for every round acquire / (prologue) / MMA / epilogue / release.
 // Called from ONE place (the phase loop of the kernel), so its code exists once.
-__device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx& c, int ph, int layer, int cta,
-                                                  float* best_val, int* best_idx, int bar) {
+// Returns the staging half whose release is left to the grid barrier (null when it was released here).
+__device__ __forceinline__ uint64_t* stream_gemv_phase(const DecodeArgs& a, StreamCtx& c, int ph, int layer, int cta,
+                                                       float* best_val, int* best_idx, int bar) {
   const PhasePlan& p = c.plan[ph];
   const ModelDims& dm = a.dims;
   const int ncols = a.ncols, nterms = a.nterms;
@@ -956,10 +993,16 @@ __device__ __forceinline__ void stream_gemv_phase(const DecodeArgs& a, StreamCtx
         }
       }
     }
+    if (r == fills - 1 && ph != kSH) {
+      if (r == 0) B2_TP(5);
+      B2_TP(6);
+      return stream_release_deferred(c);       // the grid barrier follows immediately
+    }
     stream_release(c);
     if (r == 0) B2_TP(5);
   }
   B2_TP(6);
+  return nullptr;
 }
 
 // The kernel is instantiated per cache type / head_dim / GQA group, so the loop
@@ -1010,6 +1053,7 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
     for (int cc = 0; cc < kMaxCols; ++cc) { bv[cc] = -INFINITY; bi[cc] = 0x7fffffff; }
 #pragma unroll 1
     for (int pi = 0; pi < n_phases; ++pi) {
+      uint64_t* release = nullptr;                   // staging half handed back inside the grid barrier
       int layer = pi / 5, ph = pi - layer * 5;       // A, B, C, D, E of each layer ...
       if (pi == n_phases - 1) { layer = dm.n_layers - 1; ph = kSH; }   // ... then the head
       if (ph == kSB) {
@@ -1057,9 +1101,9 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
           attn_smem_item<T, HD, G>(a, c, it, hb);
         }
         B2_TP(4);
-        stream_release(c);
+        release = stream_release_deferred(c);
       } else {
-        stream_gemv_phase(a, c, ph, layer, cta, bv, bi, bar);
+        release = stream_gemv_phase(a, c, ph, layer, cta, bv, bi, bar);
       }
       if (ph == kSH) {       // CTA-level arg-max (lowest index wins ties), one slot per CTA
         float* sv = c.s.argbuf;
@@ -1086,7 +1130,7 @@ decode_stream_kernel(const __grid_constant__ DecodeArgs a, int nsteps, unsigned 
           }
         }
       }
-      grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
+      stream_grid_barrier(a.st, &epoch, ncta, release, a.trace, bar++);
     }
     if (cta == 0) phase_argmax(a, ncta);
     grid_barrier(a.st, &epoch, ncta, a.trace, bar++);
