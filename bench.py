@@ -32,8 +32,8 @@ import __graft_entry__ as graft  # noqa: E402
 
 PREFILL_TOKENS = 1024
 DECODE_STEPS = 256
-# DRAM bytes per decode step in the ncu capture under profiles/ (a launch of two steps read 1081.4 MB and wrote 30.6 MB)
-DECODE_DRAM_BYTES_PER_STEP = 556.0e6
+# DRAM bytes per decode step in the ncu capture under profiles/ (a launch of two steps read 1082.0 MB and wrote 32.0 MB)
+DECODE_DRAM_BYTES_PER_STEP = 557.0e6
 METRIC = "decode tok/s (256 greedy steps after a 1024-token prefill), Gemma3-1B-shaped int4, batch 1 per GPU"
 
 
