@@ -946,10 +946,26 @@ __device__ inline void phase_head(const DecodeArgs& a, const DecodeSmem& s, int 
 // Final arg-max over the per-CTA candidates; optionally feeds the token back.
 __device__ __noinline__ void phase_argmax(const DecodeArgs& a, int ncta_head) {
   if (threadIdx.x < 32) {
+    // the state words are fetched up front, next to the first candidates: one L2 round trip, not a chain
+    const int sd = threadIdx.x == 0 ? __ldcg(&a.st->steps_done) : 0;
     for (int col = 0; col < a.ncols; ++col) {
+      const int pos_now = threadIdx.x == 0 ? __ldcg(&a.st->pos[col]) : 0;
+      constexpr int kPer = 8;                       // candidates a lane loads together (covers 256 CTAs)
+      float vv[kPer];
+      int ii[kPer];
+#pragma unroll
+      for (int u = 0; u < kPer; ++u) {
+        const int c = threadIdx.x + 32 * u;
+        const bool in = c < ncta_head;
+        vv[u] = in ? __ldcg(a.amax_val + (size_t)c * a.ncols + col) : -INFINITY;
+        ii[u] = in ? __ldcg(a.amax_idx + (size_t)c * a.ncols + col) : 0x7fffffff;
+      }
       float bv = -INFINITY;
       int bi = 0x7fffffff;
-      for (int c = threadIdx.x; c < ncta_head; c += 32) {
+#pragma unroll
+      for (int u = 0; u < kPer; ++u)
+        if (vv[u] > bv || (vv[u] == bv && ii[u] < bi)) { bv = vv[u]; bi = ii[u]; }
+      for (int c = threadIdx.x + 32 * kPer; c < ncta_head; c += 32) {      // grids beyond 256 CTAs
         float v = __ldcg(a.amax_val + (size_t)c * a.ncols + col);
         int i = __ldcg(a.amax_idx + (size_t)c * a.ncols + col);
         if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
@@ -962,15 +978,14 @@ __device__ __noinline__ void phase_argmax(const DecodeArgs& a, int ncta_head) {
       if (threadIdx.x == 0) {
         if (bi == 0x7fffffff) bi = 0;
         a.st->out_token[col] = bi;
-        int sd = a.st->steps_done;
         if (a.step_tokens && sd < a.step_capacity) a.step_tokens[(size_t)sd * a.ncols + col] = bi;
         if (a.advance) {
           a.st->token[col] = bi;
-          a.st->pos[col] = a.st->pos[col] + 1;
+          a.st->pos[col] = pos_now + 1;
         }
       }
     }
-    if (threadIdx.x == 0) a.st->steps_done += 1;
+    if (threadIdx.x == 0) a.st->steps_done = sd + 1;
   }
 }
 
