@@ -940,7 +940,7 @@ __device__ __forceinline__ uint64_t* stream_gemv_phase(const DecodeArgs& a, Stre
       const int ntile = fd->ntile, ktn = fd->ktn, ta = fd->ta;
       const uint4* wsm = reinterpret_cast<const uint4*>(hb);
       const float* ssm = reinterpret_cast<const float*>(hb + (size_t)ntile * ktn * 512);
-      const float* g_pre = ssm + ntile * 16;          // round 0 of norm phases: g_pre then g_post
+      const float* g_pre = ssm + ntile * 16;          // first pass of norm phases: g_pre then g_post
       const float* g_post = g_pre + dm.d;
       if (r == 0) {
         const LayerWeights& L = c.lw[layer];
