@@ -48,7 +48,10 @@ typedef struct B200LmConfig {
                               (runtime/executor/llm_executor_settings.h:95-154). */
   int32_t decode_mode;     /* B200LM_DECODE_* */
   int32_t prefill_gemm;    /* B200LM_GEMM_* */
-  int32_t reserved0;
+  int32_t page_order;      /* physical order of a session's KV pages: 0 = ascending (normal use),
+                              1 = descending.  A test hook: with the table reversed, a wrong
+                              (page, slot) computation cannot pass the KV indexing checks by
+                              accident.  Results do not depend on it. */
   void* stream;            /* cudaStream_t to run on, or NULL for an own stream */
   int32_t n_sessions;      /* sessions held by this executor, 1..4 (0 = 1); see
                               B200Lm_DecodeTokensBatch */

@@ -102,11 +102,20 @@ int B200LmOps_AttentionPrefillTc(int32_t device, const float* q, const float* k,
  * first call before starting any stream capture.  All calls on a device share
  * the array, which keeps what the last call left in it (the call itself resets
  * the one word that must start at zero); two calls whose kernels overlap on
- * the GPU -- different streams, no ordering between them -- race on it. */
+ * the GPU -- different streams, no ordering between them -- race on it.  The
+ * caller's current device is left as it was.  The per-device set-up is done
+ * under a lock, so first calls from several threads are safe. */
 int B200LmOps_AttentionDecodeStatic(int32_t device, const float* q_dev, const void* k_pages_dev,
                                     const void* v_pages_dev, const int32_t* page_table_dev, int32_t batch, int32_t s,
                                     int32_t hq, int32_t hkv, int32_t hd, int32_t window, int32_t kv_bf16,
                                     int32_t nsplit, float* out_dev, void* stream, char** err);
+
+/* Status of the work queued by B200LmOps_AttentionDecodeStatic on `stream`:
+ * waits for the stream, then reads the error word its kernels keep in the
+ * static array (no allocation either).  Returns OK, or InvalidArgument when a
+ * query position lay outside the cache; *device_error (optional) receives the
+ * raw word.  No counterpart in the reference. */
+int B200LmOps_AttentionDecodeStaticStatus(int32_t device, void* stream, int32_t* device_error, char** err);
 
 #ifdef __cplusplus
 }

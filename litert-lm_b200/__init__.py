@@ -46,7 +46,7 @@ class StatusError(RuntimeError):
 
 class B200LmConfig(C.Structure):
     _fields_ = [("struct_size", C.c_int32), ("device", C.c_int32), ("max_num_tokens", C.c_int32),
-                ("decode_mode", C.c_int32), ("prefill_gemm", C.c_int32), ("reserved0", C.c_int32),
+                ("decode_mode", C.c_int32), ("prefill_gemm", C.c_int32), ("page_order", C.c_int32),
                 ("stream", C.c_void_p), ("n_sessions", C.c_int32), ("reserved1", C.c_int32)]
 
 
@@ -59,7 +59,7 @@ _EXEC_SYMBOLS = ["B200Lm_Create", "B200Lm_CreateShared", "B200Lm_Destroy", "B200
                  "B200Lm_SelectSession", "B200Lm_GetNumSessions", "B200Lm_PrefillSession", "B200Lm_DecodeTokensBatch"]
 _OPS_SYMBOLS = ["B200LmOps_RepackW4T", "B200LmOps_RepackW4G", "B200LmOps_UnpackW4", "B200LmOps_GemvW4",
                 "B200LmOps_GemmW4", "B200LmOps_GemmGegluW4", "B200LmOps_Attention", "B200LmOps_AttentionPrefillTc",
-                "B200LmOps_AttentionDecodeStatic"]
+                "B200LmOps_AttentionDecodeStatic", "B200LmOps_AttentionDecodeStaticStatus"]
 
 
 def load_library() -> C.CDLL:
@@ -102,6 +102,7 @@ def load_library() -> C.CDLL:
         "B200LmOps_Attention": [i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, errp],
         "B200LmOps_AttentionPrefillTc": [i32, vp, vp, vp, i32, i32, i32, i32, i32, i32, vp, vp, errp],
         "B200LmOps_AttentionDecodeStatic": [i32, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i32, vp, vp, errp],
+        "B200LmOps_AttentionDecodeStaticStatus": [i32, vp, vp, errp],
     }
     for name, args in sig.items():
         fn = getattr(lib, name)
@@ -387,3 +388,11 @@ class ops:
         _call("B200LmOps_AttentionDecodeStatic", device, C.c_void_p(q_dev), C.c_void_p(k_pages_dev),
               C.c_void_p(v_pages_dev), C.c_void_p(page_table_dev), batch, s, hq, hkv, hd, window, int(kv_bf16), nsplit,
               C.c_void_p(out_dev), C.c_void_p(stream) if stream else None)
+
+    @staticmethod
+    def attention_decode_static_status(stream: int = 0, device: int = 0) -> int:
+        """Waits for `stream` and returns the device error word of the static-scratch attention
+        (0 = clean); raises StatusError when the word is set.  Allocates nothing."""
+        word = C.c_int32(-1)
+        _call("B200LmOps_AttentionDecodeStaticStatus", device, C.c_void_p(stream) if stream else None, C.byref(word))
+        return word.value

@@ -5,7 +5,10 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <map>
+#include <mutex>
 #include <string>
+#include <utility>
 
 namespace b200lm {
 
@@ -40,6 +43,25 @@ struct Error {
   do {                                                      \
     if (!(cond)) throw ::b200lm::Error{(code), (text)};    \
   } while (0)
+
+// The opt-in dynamic shared-memory limit of a kernel is a property of (kernel, device), shared by every
+// caller in the process.  It is only ever RAISED here: lowering it for one caller's smaller shape would
+// make a later launch that asks for more fail.  Thread-safe.
+inline void raise_dyn_smem(const void* kernel, size_t bytes) {
+  static std::mutex mu;
+  static std::map<std::pair<const void*, int>, size_t> high;
+  int dev = 0;
+  B2_CUDA(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(mu);
+  size_t& h = high[std::make_pair(kernel, dev)];
+  if (bytes <= h) return;
+  B2_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes));
+  h = bytes;
+}
+template <typename... KArgs>
+inline void raise_dyn_smem(void (*kernel)(KArgs...), size_t bytes) {
+  raise_dyn_smem(reinterpret_cast<const void*>(kernel), bytes);
+}
 
 constexpr int kPage = 256;       // KV positions per page
 constexpr int kMaxBuckets = 8;

@@ -288,8 +288,8 @@ void launch_gemm(cudaStream_t st, int mode, const CUtensorMap& a_map, const __nv
     B2_CUDA(cudaGetDevice(&dev));
     B2_CHECK(dev >= 0 && dev < 64, kInternal, "device ordinal out of range");
     if (!sms_of[dev]) {
-      B2_CUDA(cudaFuncSetAttribute(gemm_w4_ts_kernel<0>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsSmem));
-      B2_CUDA(cudaFuncSetAttribute(gemm_w4_ts_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kTsSmem));
+      raise_dyn_smem(gemm_w4_ts_kernel<0>, (size_t)(kTsSmem));
+      raise_dyn_smem(gemm_w4_ts_kernel<1>, (size_t)(kTsSmem));
       B2_CUDA(cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev));
     }
     const int sms = sms_of[dev];
@@ -315,6 +315,8 @@ Executor::~Executor() {
   if (stream) cudaStreamSynchronize(stream);
   if (graph_exec) cudaGraphExecDestroy(graph_exec);
   for (void* p : allocations) cudaFree(p);
+  for (int i = 0; i < kTokRing; ++i)
+    if (tok_ring_done[i]) cudaEventDestroy(tok_ring_done[i]);
   if (pinned) cudaFreeHost(pinned);
   if (own_stream && stream) cudaStreamDestroy(stream);
 }
@@ -352,6 +354,7 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
                                                           : cfg.prefill_gemm;
   B2_CHECK(e->prefill_gemm != B200LM_GEMM_TCGEN05 || model->has_tc, kFailedPrecondition,
            "tensor-core GEMM weights were not loaded for this model");
+  B2_CHECK(cfg.page_order == 0 || cfg.page_order == 1, kInvalidArgument, "page_order must be 0 or 1");
   e->decode_mode = cfg.decode_mode == B200LM_DECODE_AUTO ? B200LM_DECODE_PERSISTENT : cfg.decode_mode;
   const int esz = d.kv_dtype == 0 ? 4 : 2;
   // ---- paged KV cache
@@ -384,7 +387,7 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   for (int sn = 0; sn < e->n_sessions; ++sn)
     for (int i = 0; i < e->pages_per_seq; ++i)
       e->page_table_host[(size_t)sn * e->pages_per_seq + i] =
-          sn * e->pages_per_seq + ((cfg.reserved0 & 1) ? e->pages_per_seq - 1 - i : i);   // bit 0: reversed page order
+          sn * e->pages_per_seq + (cfg.page_order == 1 ? e->pages_per_seq - 1 - i : i);
   int* ptd = reinterpret_cast<int*>(e->alloc(sizeof(int) * total_pages, false));
   B2_CUDA(cudaMemcpy(ptd, e->page_table_host.data(), sizeof(int) * total_pages, cudaMemcpyHostToDevice));
   e->page_table_dev = ptd;
@@ -443,8 +446,8 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   e->dec_smem = dec_smem_bytes(d, e->decode_mode == B200LM_DECODE_PERSISTENT ? 1 : e->n_sessions);
   B2_CHECK(e->dec_smem <= (size_t)prop.sharedMemPerBlockOptin, kUnimplemented,
            "decode kernels need more shared memory than the device offers");
-  B2_CUDA(cudaFuncSetAttribute(decode_phase_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->dec_smem));
-  B2_CUDA(cudaFuncSetAttribute(decode_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->dec_smem));
+  raise_dyn_smem(decode_phase_kernel, (size_t)(e->dec_smem));
+  raise_dyn_smem(decode_persistent_kernel, (size_t)(e->dec_smem));
   if (e->decode_mode == B200LM_DECODE_PERSISTENT) {
     // staging halves take what shared memory the activation staging leaves, up to 96 KiB each
     size_t fixed = stream_fixed_bytes(d, e->n_sessions);
@@ -456,7 +459,7 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
       e->stream_half = half;
       e->stream_smem = fixed + 2 * (size_t)half;
       const void* kfn = decode_stream_kernel_for(d);
-      B2_CUDA(cudaFuncSetAttribute(kfn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)e->stream_smem));
+      raise_dyn_smem(kfn, (size_t)(e->stream_smem));
       cudaFuncAttributes fa;
       B2_CUDA(cudaFuncGetAttributes(&fa, kfn));
       int occ = (size_t)fa.maxThreadsPerBlock >= (size_t)kStreamThreads ? 1 : 0;
@@ -504,20 +507,24 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
       e->tm_vt.push_back(make_bf16_map(e->kv_host[i].v16, 2, vd, vs, vb));
     }
     if (d.hd == 256)
-      B2_CUDA(cudaFuncSetAttribute(flash_prefill_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<256>::kTotal));
+      raise_dyn_smem(flash_prefill_tc_kernel<256>, (size_t)(FaSmem<256>::kTotal));
     else
-      B2_CUDA(cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<128>::kTotal));
+      raise_dyn_smem(flash_prefill_tc_kernel<128>, (size_t)(FaSmem<128>::kTotal));
   }
+  raise_dyn_smem(pf_attn_kernel, sizeof(float) * ((size_t)(d.group() + 2) * d.hd + (size_t)8 * d.group() * (d.hd + 2)));
   if (e->prefill_gemm == B200LM_GEMM_TCGEN05) {
     e->tm_h = make_activation_map(e->pf_h, (int)tp, d.d);
     e->tm_attn = make_activation_map(e->pf_attn, (int)tp, d.nq());
     e->tm_act = make_activation_map(e->pf_act, (int)tp, d.ffn);
   }
-  size_t pin = sizeof(float) * (size_t)d.vocab + sizeof(int) * (tp + (size_t)d.max_ctx * kMaxCols) + 4096;
+  // page-locked staging: logits | kTokRing slices of prompt ids | sampled ids of a decode call | state words
+  size_t pin = sizeof(float) * (size_t)d.vocab + sizeof(int) * (kTokRing * tp + (size_t)d.max_ctx * kMaxCols) + 4096;
   B2_CUDA(cudaMallocHost(&e->pinned, pin));
   e->pin_logits = reinterpret_cast<float*>(e->pinned);
   e->pin_ints = reinterpret_cast<int*>(e->pin_logits + d.vocab);
-  e->pin_state = reinterpret_cast<DecodeState*>(e->pin_ints + tp + (size_t)d.max_ctx * kMaxCols);
+  e->pin_steps = e->pin_ints + (size_t)kTokRing * tp;
+  e->pin_state = reinterpret_cast<DecodeState*>(e->pin_steps + (size_t)d.max_ctx * kMaxCols);
+  for (int i = 0; i < kTokRing; ++i) B2_CUDA(cudaEventCreateWithFlags(&e->tok_ring_done[i], cudaEventDisableTiming));
   B2_CUDA(cudaDeviceSynchronize());
   return e;
 }
@@ -580,8 +587,20 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
   B2_CHECK(start + T <= max_num_tokens, kInvalidArgument,
            "Input token ids are too long. Exceeding the maximum number of tokens allowed: " +
                std::to_string(start + T) + " > " + std::to_string(max_num_tokens));
-  memcpy(pin_ints, tokens, sizeof(int) * T);
-  B2_CUDA(cudaMemcpyAsync(pf_tokens, pin_ints, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
+  // Token ids go through a ring of page-locked slices, one per queued chunk: a slice is rewritten only
+  // after the host-to-device copy that reads it has completed (its event), so chunks queued back to
+  // back without a wait (several work groups, wait_for_completion = false) never share staging memory.
+  {
+    const int slot = tok_ring_next;
+    tok_ring_next = (tok_ring_next + 1) % kTokRing;
+    if (tok_ring_used[slot]) B2_CUDA(cudaEventSynchronize(tok_ring_done[slot]));
+    int* stage = pin_ints + (size_t)slot * t_pad;
+    memcpy(stage, tokens, sizeof(int) * T);
+    // the device-side id buffer is read by the first kernel of the chunk only; chunks are stream-ordered
+    B2_CUDA(cudaMemcpyAsync(pf_tokens, stage, sizeof(int) * T, cudaMemcpyHostToDevice, stream));
+    B2_CUDA(cudaEventRecord(tok_ring_done[slot], stream));
+    tok_ring_used[slot] = true;
+  }
   h2d_bytes += sizeof(int) * (size_t)T;
   int* err = &dargs.st->err;
   const int* ptab = page_table_dev + (size_t)active * pages_per_seq;     // the active session's pages
@@ -592,7 +611,6 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
   ++launches;
   const int mode = prefill_gemm;
   const size_t attn_smem = sizeof(float) * ((size_t)(d.group() + 2) * d.hd + (size_t)8 * d.group() * (d.hd + 2));
-  B2_CUDA(cudaFuncSetAttribute(pf_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem));
   for (int li = 0; li < d.n_layers; ++li) {
     const LayerWeights& L = model->layers_host[li];
     const LayerGemmWeights& Gm = model->gemm_host[li];
@@ -674,13 +692,7 @@ void Executor::prefill_group(const int* ids, int len) {
     ++current_step;
   }
   next_input_token = ids[len - 1];
-  if (!run.empty()) {
-    try {
-      run_prefill_chunk(run.data(), (int)run.size(), start);
-    } catch (...) {
-      throw;
-    }
-  }
+  if (!run.empty()) run_prefill_chunk(run.data(), (int)run.size(), start);
 }
 
 void Executor::prefill(const int* ids, int n, bool wait, const volatile int* cancel) {
@@ -802,7 +814,7 @@ void Executor::decode_tokens(int nsteps, int* out_ids) {
   int id = take_decode_id(nullptr);
   push_decode_state(&id, &current_step, 1);
   launch_decode_steps(nsteps);
-  int* dst = pin_ints + t_pad;
+  int* dst = pin_steps;
   B2_CUDA(cudaMemcpyAsync(dst, dargs.step_tokens, sizeof(int) * (size_t)nsteps, cudaMemcpyDeviceToHost, stream));
   d2h_bytes += sizeof(int) * (size_t)nsteps;
   check_device_error("Decode");
@@ -834,7 +846,7 @@ void Executor::decode_tokens_batch(int nsteps, int* out_ids) {
   }
   push_decode_state(tok, pos, n_sessions);
   launch_decode_steps(nsteps, n_sessions, 0);
-  int* dst = pin_ints + t_pad;
+  int* dst = pin_steps;
   B2_CUDA(cudaMemcpyAsync(dst, dargs.step_tokens, sizeof(int) * (size_t)nsteps * n_sessions, cudaMemcpyDeviceToHost,
                           stream));
   d2h_bytes += sizeof(int) * (size_t)nsteps * n_sessions;

@@ -210,7 +210,7 @@ int B200LmOps_GemvW4(int32_t device, const uint8_t* packed, const float* scale, 
   dm.d = (int)k; dm.ffn = (int)k; dm.hq = 1; dm.hkv = 1; dm.hd = 32;
   size_t smem = dec_smem_bytes(dm, ncols);
   B2_CHECK(smem <= (size_t)prop.sharedMemPerBlockOptin, kInvalidArgument, "k too large for the shared-memory staging");
-  B2_CUDA(cudaFuncSetAttribute(gemv_w4_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  raise_dyn_smem(gemv_w4_kernel, (size_t)(smem));
   GemvJob j{w.as<uint4>(), sc.as<float>(), (int)n, (int)k, kslices, yd.as<float>(), kEpiPlain};
   gemv_w4_kernel<<<prop.multiProcessorCount, kDecThreads, smem>>>(j, xd.as<float>(), ncols, nterms, dm);
   B2_CUDA(cudaGetLastError());
@@ -410,8 +410,8 @@ int B200LmOps_Attention(int32_t device, const float* q, const float* k, const fl
   B2_CUDA(cudaEventCreate(&e1));
   size_t smem_pf = sizeof(float) * ((size_t)(G + 2) * hd + (size_t)8 * G * (hd + 2));
   size_t smem_dec = sizeof(float) * ((size_t)(G + 2) * hd + (size_t)kDecWarps * G * (hd + 2));
-  B2_CUDA(cudaFuncSetAttribute(pf_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_pf));
-  B2_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec));
+  raise_dyn_smem(pf_attn_kernel, (size_t)(smem_pf));
+  raise_dyn_smem(attn_decode_kernel, (size_t)(smem_dec));
   auto run = [&]() {
     if (decode) {
       j.part_o = po.as<float>();
@@ -513,9 +513,9 @@ int B200LmOps_AttentionPrefillTc(int32_t device, const float* q, const float* k,
   const int TT = 128 / G;
   dim3 grid((s + TT - 1) / TT, hkv);
   if (hd == 256)
-    B2_CUDA(cudaFuncSetAttribute(flash_prefill_tc_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<256>::kTotal));
+    raise_dyn_smem(flash_prefill_tc_kernel<256>, (size_t)(FaSmem<256>::kTotal));
   else
-    B2_CUDA(cudaFuncSetAttribute(flash_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, FaSmem<128>::kTotal));
+    raise_dyn_smem(flash_prefill_tc_kernel<128>, (size_t)(FaSmem<128>::kTotal));
   auto run = [&]() {
     if (hd == 256) flash_prefill_tc_kernel<256><<<grid, kFaThreads, FaSmem<256>::kTotal>>>(tm_q, tm_k, tm_vt, fa);
     else flash_prefill_tc_kernel<128><<<grid, kFaThreads, FaSmem<128>::kTotal>>>(tm_q, tm_k, tm_vt, fa);

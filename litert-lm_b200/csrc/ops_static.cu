@@ -15,6 +15,8 @@
 #include "decode_ops.cuh"
 #include "prefill_ops.cuh"
 
+#include <mutex>
+
 namespace b200lm {
 
 constexpr size_t kStaticScratchBytes = 8u << 20;          // 8 MiB per GPU
@@ -36,22 +38,53 @@ __global__ void static_scratch_prepare_kernel(int nq, int pos) {
 
 constexpr int kMaxDevices = 64;
 static unsigned char* g_static_scratch_addr[kMaxDevices] = {nullptr};
+static std::mutex g_static_scratch_mu;     // guards the per-device set-up below
 
 // Device address of the array on `device` (which must be current).  Looked up
-// once per device.
+// once per device, under a lock: concurrent first calls do the set-up once.
 static unsigned char* static_scratch_for(int device) {
   B2_CHECK(device >= 0 && device < kMaxDevices, kInvalidArgument, "device ordinal out of range");
+  std::lock_guard<std::mutex> lock(g_static_scratch_mu);
   if (!g_static_scratch_addr[device]) {
     void* p = nullptr;
     cudaError_t e = cudaGetSymbolAddress(&p, g_attn_static_scratch);
     if (e != cudaSuccess || p == nullptr)
       throw Error{kInternal, std::string("cudaGetSymbolAddress(static scratch): ") + cudaGetErrorString(e)};
-    // attribute changes, not allocations; done with the set-up so later calls only launch
-    size_t smem_dec = sizeof(float) * ((size_t)(4 + 2) * 256 + (size_t)kDecWarps * 4 * (256 + 2));
-    B2_CUDA(cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_dec));
+    // attribute change, not an allocation; done with the set-up so later calls only launch.  The limit is
+    // raised to the largest shape the entry point accepts and never lowered by any other caller.
+    raise_dyn_smem(attn_decode_kernel, sizeof(float) * ((size_t)(4 + 2) * 256 + (size_t)kDecWarps * 4 * (256 + 2)));
     g_static_scratch_addr[device] = reinterpret_cast<unsigned char*>(p);
   }
   return g_static_scratch_addr[device];
+}
+
+// Makes `device` current for the duration of a call and puts the caller's device back afterwards.
+struct DeviceScope {
+  int prev = -1;
+  explicit DeviceScope(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) { cudaGetLastError(); prev = -1; }
+    B2_CUDA(cudaSetDevice(device));
+  }
+  ~DeviceScope() {
+    if (prev >= 0) cudaSetDevice(prev);
+  }
+};
+
+static int static_fail(char** err, int code, const std::string& msg) {
+  if (err) {
+    *err = reinterpret_cast<char*>(malloc(msg.size() + 1));
+    if (*err) memcpy(*err, msg.c_str(), msg.size() + 1);
+  }
+  return code;
+}
+
+static void require_device(int device) {
+  int ndev = 0;
+  if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
+    cudaGetLastError();
+    throw Error{kFailedPrecondition, "no CUDA device: this backend has no CPU fallback"};
+  }
+  B2_CHECK(device >= 0 && device < ndev, kInvalidArgument, "device ordinal out of range");
 }
 
 }  // namespace b200lm
@@ -78,19 +111,15 @@ extern "C" int B200LmOps_AttentionDecodeStatic(int32_t device, const float* q_de
     B2_CHECK(kStaticHeaderBytes + part_o_bytes + part_ml_bytes <= kStaticScratchBytes, kInvalidArgument,
              "split partials need " + std::to_string(part_o_bytes + part_ml_bytes) + " bytes; the static scratch holds " +
                  std::to_string(kStaticScratchBytes - kStaticHeaderBytes) + " (lower batch or nsplit)");
-    int ndev = 0;
-    if (cudaGetDeviceCount(&ndev) != cudaSuccess || ndev <= 0) {
-      cudaGetLastError();
-      throw Error{kFailedPrecondition, "no CUDA device: this backend has no CPU fallback"};
-    }
-    B2_CHECK(device < ndev, kInvalidArgument, "device ordinal out of range");
-    B2_CUDA(cudaSetDevice(device));
+    require_device(device);
+    DeviceScope scope(device);                                  // the caller's current device is restored on return
     unsigned char* scratch = static_scratch_for(device);        // first call on a device does the set-up
     cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
     int* hdr = reinterpret_cast<int*>(scratch);
     float* part_o = reinterpret_cast<float*>(scratch + kStaticHeaderBytes);
     float* part_ml = reinterpret_cast<float*>(scratch + kStaticHeaderBytes + part_o_bytes);
     static_scratch_prepare_kernel<<<(batch + 255) / 256, 256, 0, st>>>(batch, s - 1);
+    B2_CUDA(cudaGetLastError());
     ModelDims dm{};
     dm.hq = hq; dm.hkv = hkv; dm.hd = hd; dm.d = 64; dm.ffn = 64;
     dm.window = window > 0 ? window : 1 << 30;
@@ -119,17 +148,38 @@ extern "C" int B200LmOps_AttentionDecodeStatic(int32_t device, const float* q_de
     const int items = batch * hkv * nsplit;
     const int grid = items < n_sms ? items : n_sms;
     attn_decode_kernel<<<grid, kDecThreads, smem_dec, st>>>(dm, j, batch);
+    B2_CUDA(cudaGetLastError());         // a rejected launch must not be followed by a combine of stale partials
     const int total = batch * hq * hd;
     attn_combine_kernel<<<(total + 255) / 256, 256, 0, st>>>(part_o, part_ml, batch, hq, hkv, hd, nsplit, out_dev);
     B2_CUDA(cudaGetLastError());
   } catch (const Error& e_) {
-    if (err) {
-      *err = reinterpret_cast<char*>(malloc(e_.msg.size() + 1));
-      if (*err) memcpy(*err, e_.msg.c_str(), e_.msg.size() + 1);
-    }
-    return e_.code;
+    return static_fail(err, e_.code, e_.msg);
   } catch (...) {
-    return kInternal;
+    return static_fail(err, kInternal, "unknown failure");
+  }
+  return kOk;
+}
+
+// Reads back the error word that the kernels of B200LmOps_AttentionDecodeStatic write into the static
+// array (a query position outside the cache).  Waits for `stream`, allocates nothing.
+extern "C" int B200LmOps_AttentionDecodeStaticStatus(int32_t device, void* stream, int32_t* device_error, char** err) {
+  if (err) *err = nullptr;
+  try {
+    require_device(device);
+    DeviceScope scope(device);
+    (void)static_scratch_for(device);
+    cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+    int word = 0;
+    B2_CUDA(cudaMemcpyFromSymbolAsync(&word, g_attn_static_scratch, sizeof(int), 0, cudaMemcpyDeviceToHost, st));
+    B2_CUDA(cudaStreamSynchronize(st));
+    if (device_error) *device_error = word;
+    if (word == kDevBadPosition) throw Error{kInvalidArgument, "a query position lay outside the cache"};
+    if (word == kDevBarrierTimeout) throw Error{kDeadlineExceeded, "a bounded device-side wait gave up"};
+    if (word != kDevOk) throw Error{kInternal, "device error word " + std::to_string(word)};
+  } catch (const Error& e_) {
+    return static_fail(err, e_.code, e_.msg);
+  } catch (...) {
+    return static_fail(err, kInternal, "unknown failure");
   }
   return kOk;
 }

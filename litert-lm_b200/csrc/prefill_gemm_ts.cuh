@@ -107,10 +107,6 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
   const int t_tiles = (g.T + kTsTok - 1) / kTsTok;
   const int total = n_tiles * t_tiles * g.ksplit;
   const int my_tiles = (int)blockIdx.x < total ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
-#ifdef B2_GEMM_TRACE
-  const int gt_slot = blockIdx.x == 0 ? 0 : (blockIdx.x == gridDim.x - 1 ? 1 : -1);
-#endif
-  if (threadIdx.x == 0) B2_GT(0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -131,7 +127,6 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
   // barriers and TMEM are set up: from here on the kernel reads what its predecessor wrote
   pdl_wait();
   pdl_launch_dependents();
-  if (threadIdx.x == 0) B2_GT(1);
 
   if (warp == 0) {
     // ---- producer: one elected lane issues the copies, the warp stays together
@@ -144,7 +139,6 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
         const int s = it % S, n = it / S;
         if (n > 0) ok = mbar_wait(&empty_bar[s], (n - 1) & 1, g.err);
         if (ok && lane == 0) {
-          if (it < 112) B2_GT(16 + it);
           mbar_arrive_expect_tx(&full_bar[s], kTsStageBytes);
 #pragma unroll
           for (int h = 0; h < kTsTok / 128; ++h)
@@ -169,7 +163,6 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
-          if (it < 112) B2_GT(128 + it);
           const uint64_t xd = umma_desc_sw128(smem_u32(sX + s * kTsStageX));
 #pragma unroll
           for (int k = 0; k < kGemmBK / 16; ++k)   // 16 bf16 along K per MMA: 8 TMEM columns, 32 bytes of X
@@ -194,7 +187,6 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
       ok = mbar_wait(&full_bar[s], n & 1, g.err);
       if (ok && n > 0) ok = mbar_wait(&empty_bar[s], (n - 1) & 1, g.err);
       if (!ok) break;
-      if (threadIdx.x == 64 && it < 112) B2_GT(256 + it);
       tc_fence_after();
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
@@ -216,7 +208,6 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&deq_bar[s]);
-      if (threadIdx.x == 64 && it < 112) B2_GT(384 + it);
     }
   } else {
     // ---- epilogue: this warp takes 64 token columns of its 32 weight rows
@@ -272,12 +263,10 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
           if (32 + c < tlim && f < F) dst[(size_t)(32 + c) * F] = __float2bfloat16(gelu_tanh_fast(gate) * up);
         }
       }
-      if (threadIdx.x == 64 + 32 * kTsDeqWarps && li < 8) B2_GT(8 + li);
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (threadIdx.x == 0) B2_GT(3);
   if (*reinterpret_cast<volatile int*>(g.err) == (int)kDevBarrierTimeout) {
     // a wait gave up: let any bulk copy still in flight land before the CTA retires
     for (int i = 0; i < 2000; ++i) __nanosleep(100);

@@ -464,15 +464,6 @@ struct GemmArgs {
   float* outF;             // epilogue 0
   __nv_bfloat16* outB;     // epilogue 1 (GeGLU): [T][N/2]
   int* err;
-#ifdef B2_GEMM_TRACE
-  long long* trace;        // development builds only: clock stamps of the first and the last CTA
-#endif
 };
-
-#ifdef B2_GEMM_TRACE
-#define B2_GT(i) do { if (g.trace && gt_slot >= 0) g.trace[gt_slot * 512 + (i)] = clock64(); } while (0)
-#else
-#define B2_GT(i) do { } while (0)
-#endif
 
 }  // namespace b200lm

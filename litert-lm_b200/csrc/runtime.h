@@ -125,9 +125,14 @@ class Executor {
   CUtensorMap tm_q{};
   std::vector<CUtensorMap> tm_k, tm_vt;   // per layer
   // pinned staging
+  static constexpr int kTokRing = 4;    // prompt-id slices that may be queued for upload at once
   void* pinned = nullptr;
   float* pin_logits = nullptr;
-  int* pin_ints = nullptr;
+  int* pin_ints = nullptr;          // kTokRing slices of t_pad ids
+  int* pin_steps = nullptr;         // ids sampled by a multi-step decode call
+  cudaEvent_t tok_ring_done[kTokRing] = {nullptr, nullptr, nullptr, nullptr};
+  bool tok_ring_used[kTokRing] = {false, false, false, false};
+  int tok_ring_next = 0;
   DecodeState* pin_state = nullptr;
 };
 

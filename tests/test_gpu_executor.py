@@ -166,3 +166,64 @@ def test_prefill_in_pieces_equals_one_call(pkg, models):
     cos, err = logits_close(lb, lc)
     assert cos >= 0.9999 and err <= 5e-3
     assert b.GetCurrentStep() == c.GetCurrentStep() == a.GetCurrentStep() - 1
+
+
+def test_unwaited_prefill_of_several_work_groups_matches_oracle(pkg, orc, models):
+    """Prefill(wait_for_completion=False) of a prompt that plans three or more work groups, then a
+    second unwaited Prefill: every chunk's ids travel through page-locked staging while earlier
+    chunks are still queued, so a staging slice that were reused too early would embed wrong ids."""
+    cfg, rec, img = models("small")                 # buckets 256 / 64 / 16
+    prompt = seeded_ids(5, cfg.vocab, 700)          # 256 + 256 + 188 -> three groups
+    more = seeded_ids(6, cfg.vocab, 90)
+    ex = pkg.B200LlmExecutor(img)
+    ref = orc.OracleExecutor(orc.OracleModel(rec))
+    ex.Prefill(prompt, wait_for_completion=False)
+    assert len(ex.GetLastPrefillPlan()) >= 3
+    ex.Prefill(more, wait_for_completion=False)     # queued behind the first call
+    assert ref.prefill(prompt) == 0 and ref.prefill(more) == 0
+    tok = None
+    for step in range(4):
+        got = ex.DecodeLogits(tok).ravel()
+        rc, want = ref.decode_logits(tok)
+        assert rc == 0
+        cos, err = logits_close(got, want)
+        assert cos >= COS_MIN and err <= ERR_MAX, (step, cos, err)
+        tok = int(orc.greedy(want)[0])
+        assert int(np.argmax(got)) == tok
+    for pos in (3, 260, 600, 750):                  # rows of every chunk
+        row, _, _ = ex.ReadKvRow(0, False, 0, pos)
+        want = ref.read_kv(0, False, 0, pos)
+        assert np.abs(row[:cfg.head_dim] - want).max() <= 2e-2 * max(1.0, np.abs(want).max()), pos
+
+
+def test_greedy_ties_pick_the_lowest_index(pkg, orc, mio):
+    """Vocabulary rows with identical int4 codes and scales give bit-identical logits (the GEMV
+    accumulates in integers), so planting copies of a row plants exact ties: in one 16-row tile,
+    in neighbouring tiles, and in the ranges of different CTAs.  The device arg-max must return
+    the lowest index of the maximum, as std::max_element does in the reference's greedy branch
+    (runtime/components/sampling_cpu_util.cc:32-41)."""
+    cfg = mio.config_small()
+    tensors = dict(mio.generate_tensors(cfg))
+    eq, es = tensors["embed.q"].copy(), tensors["embed.scale"].copy()
+    groups = []
+    for base in (40, 700, 1500, 2300, 3100):
+        members = [base, base + 1, base + 16, base + 37, (base + 2048) % cfg.vocab, (base + 3333) % cfg.vocab]
+        for m in members[1:]:
+            eq[m] = eq[base]
+        es[members] = es[base] * 6.0                # loud rows: one of the groups holds the maximum
+        groups.append(sorted(members))
+    tensors["embed.q"], tensors["embed.scale"] = eq, es
+    rec = mio.pack_weights_record(cfg, tensors)
+    img = mio.export_model_litertlm(cfg, rec)
+    prompt = seeded_ids(9, cfg.vocab, 40)
+    ref = orc.OracleExecutor(orc.OracleModel(rec))
+    assert ref.prefill(prompt) == 0
+    want = [ref.decode_token()[1] for _ in range(16)]
+    for mode in (2, 1):
+        ex = pkg.B200LlmExecutor(img, decode_mode=mode)
+        ex.Prefill(prompt)
+        got = list(ex.DecodeTokens(16))
+        assert got == want, (mode, got, want)
+    tied = [t for t in want if any(t in g for g in groups)]
+    assert tied, "no planted row won a step: the case does not exercise ties"
+    assert all(t == g[0] for t in tied for g in groups if t in g)     # always the lowest member

@@ -1,6 +1,7 @@
 """Parity at the per-layer geometry of the two larger benchmark shapes (4B: hidden 2560, 8 query /
 4 kv heads of 256, ffn 10240; 27B: hidden 5376, 32 query / 16 kv heads of 128, ffn 21504), on
-slices of a few layers so the CPU oracle keeps up.  One GPU, no tensor parallelism."""
+slices of a few layers so the CPU oracle keeps up.  One GPU, no tensor parallelism.  The prompts
+are longer than the 1024-position window, so the local layers really drop keys."""
 import numpy as np
 import pytest
 
@@ -11,7 +12,7 @@ pytestmark = pytest.mark.gpu
 COS_MIN, ERR_MAX = 0.999, 2e-2
 
 
-@pytest.mark.parametrize("name,prompt_len", [("gemma3-4b-slice", 300), ("gemma3-27b-slice", 200)])
+@pytest.mark.parametrize("name,prompt_len", [("gemma3-4b-slice", 1100), ("gemma3-27b-slice", 1100)])
 def test_logits_and_tokens_match_oracle_on_large_layer_shapes(pkg, orc, models, name, prompt_len):
     cfg, rec, img = models(name)
     prompt = seeded_ids(51, cfg.vocab, prompt_len)

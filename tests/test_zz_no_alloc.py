@@ -27,7 +27,7 @@ def to_pages(x, hkv, hd, bf16):
 
 
 @pytest.mark.parametrize("hq,hkv,hd,window,kv_bf16,nsplit", [(4, 1, 256, 0, False, 16), (8, 4, 128, 48, True, 4)])
-def test_static_scratch_attention_matches_allocating_entry_point(pkg, hq, hkv, hd, window, kv_bf16, nsplit):
+def test_static_scratch_attention_matches_allocating_entry_point(pkg, orc, hq, hkv, hd, window, kv_bf16, nsplit):
     import torch
     rng = np.random.Generator(np.random.PCG64(17))
     for call, (batch, s) in enumerate([(3, 700), (2, 333)]):          # two calls in a row, different shapes
@@ -48,6 +48,21 @@ def test_static_scratch_attention_matches_allocating_entry_point(pkg, hq, hkv, h
         got = out.cpu().numpy()
         assert np.isfinite(got).all(), call
         assert np.abs(got - want).max() < 2e-4, (call, np.abs(got - want).max())
+        assert pkg.ops.attention_decode_static_status() == 0          # the error word its kernels keep is clean
+        # ... and against the CPU oracle directly (every query sits at position s - 1); a bf16 cache
+        # carries the rounding of K and V, so the oracle sees the rounded rows
+        if kv_bf16:
+            k = torch.from_numpy(k).to(torch.bfloat16).float().numpy()
+            v = torch.from_numpy(v).to(torch.bfloat16).float().numpy()
+        for b in range(batch):
+            ref = orc.attention(q[b:b + 1], k, v, s - 1, window)
+            assert np.abs(got[b:b + 1] - ref).max() < 2e-4, (call, b, np.abs(got[b:b + 1] - ref).max())
+        # the allocating entry point at a much smaller shape in between: it must not shrink a kernel
+        # limit that the next static call (head_dim 256, group of 4) depends on
+        qs = rng.standard_normal((1, 1, 32), dtype=np.float32)
+        ks = rng.standard_normal((40, 1, 32), dtype=np.float32)
+        small, _ = pkg.ops.attention(qs, ks, ks, nsplit=2)
+        assert np.abs(small - orc.attention(qs, ks, ks, 39, 0)).max() < 2e-4
 
 
 def test_static_scratch_limits_are_enforced(pkg):
