@@ -30,13 +30,16 @@ extern "C" {
 
 typedef struct B200LmExecutor B200LmExecutor;
 
-/* decode_mode: AUTO picks the streaming persistent kernel when the model fits its
- * shared-memory staging, else one kernel per phase replayed from a CUDA graph. */
+/* decode_mode: AUTO picks the chained persistent kernel when the model fits its
+ * shared-memory ring, else the streaming persistent kernel, else one kernel per
+ * phase replayed from a CUDA graph. */
 enum {
   B200LM_DECODE_AUTO = 0,
   B200LM_DECODE_PHASE_KERNELS = 1,     /* one kernel per phase, CUDA graph per step */
-  B200LM_DECODE_PERSISTENT = 2,        /* one cooperative kernel, weights streamed by bulk async copies */
-  B200LM_DECODE_PERSISTENT_BASIC = 3   /* one cooperative kernel, plain loads (comparison) */
+  B200LM_DECODE_PERSISTENT = 2,        /* one cooperative kernel, grid barrier per phase, weights streamed by bulk async copies */
+  B200LM_DECODE_PERSISTENT_BASIC = 3,  /* one cooperative kernel, grid barrier per phase, plain loads (comparison) */
+  B200LM_DECODE_CHAINED = 4            /* one cooperative kernel without grid barriers: phases hand results over in
+                                          flag-carrying words, gate/up + down fused */
 };
 enum { B200LM_GEMM_AUTO = 0, B200LM_GEMM_CHECK = 1, B200LM_GEMM_TCGEN05 = 2 };
 
@@ -130,6 +133,11 @@ int B200Lm_Reset(B200LmExecutor* e, char** err);
 int B200Lm_GetVocabSize(B200LmExecutor* e, int32_t* out, char** err);
 int B200Lm_GetCurrentStep(B200LmExecutor* e, int32_t* out, char** err);
 int B200Lm_GetMaxNumTokens(B200LmExecutor* e, int32_t* out, char** err);
+
+/* The decode path this executor settled on (B200LM_DECODE_*): what AUTO resolved to, or
+ * the fallback taken when the requested kernel does not fit the model.  No counterpart
+ * in the reference. */
+int B200Lm_GetDecodeMode(B200LmExecutor* e, int32_t* out, char** err);
 
 /* ExecutorBackendName() (runtime/executor/llm_executor_base.h:79). */
 const char* B200Lm_BackendName(void);

@@ -31,7 +31,7 @@ FAILED_PRECONDITION, OUT_OF_RANGE, UNIMPLEMENTED, INTERNAL = 9, 11, 12, 13
 _CODE_NAMES = {0: "OK", 1: "CANCELLED", 3: "INVALID_ARGUMENT", 4: "DEADLINE_EXCEEDED", 5: "NOT_FOUND",
                9: "FAILED_PRECONDITION", 11: "OUT_OF_RANGE", 12: "UNIMPLEMENTED", 13: "INTERNAL"}
 
-DECODE_AUTO, DECODE_PHASE_KERNELS, DECODE_PERSISTENT, DECODE_PERSISTENT_BASIC = 0, 1, 2, 3
+DECODE_AUTO, DECODE_PHASE_KERNELS, DECODE_PERSISTENT, DECODE_PERSISTENT_BASIC, DECODE_CHAINED = 0, 1, 2, 3, 4
 GEMM_AUTO, GEMM_CHECK, GEMM_TCGEN05 = 0, 1, 2
 
 
@@ -54,7 +54,7 @@ _lib: Optional[C.CDLL] = None
 
 _EXEC_SYMBOLS = ["B200Lm_Create", "B200Lm_CreateShared", "B200Lm_Destroy", "B200Lm_Prefill", "B200Lm_DecodeLogits",
                  "B200Lm_DecodeToken", "B200Lm_DecodeTokens", "B200Lm_Reset", "B200Lm_GetVocabSize",
-                 "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_BackendName", "B200Lm_Synchronize",
+                 "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_GetDecodeMode", "B200Lm_BackendName", "B200Lm_Synchronize",
                  "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount", "B200Lm_TraceDecodeStep",
                  "B200Lm_SelectSession", "B200Lm_GetNumSessions", "B200Lm_PrefillSession", "B200Lm_DecodeTokensBatch"]
 _OPS_SYMBOLS = ["B200LmOps_RepackW4T", "B200LmOps_RepackW4G", "B200LmOps_UnpackW4", "B200LmOps_GemvW4",
@@ -84,6 +84,7 @@ def load_library() -> C.CDLL:
         "B200Lm_GetVocabSize": [vp, vp, errp],
         "B200Lm_GetCurrentStep": [vp, vp, errp],
         "B200Lm_GetMaxNumTokens": [vp, vp, errp],
+        "B200Lm_GetDecodeMode": [vp, vp, errp],
         "B200Lm_Synchronize": [vp, errp],
         "B200Lm_GetLastPrefillPlan": [vp, vp, vp, i32, vp, errp],
         "B200Lm_ReadKvRow": [vp, i32, i32, i32, i32, vp, vp, vp, errp],
@@ -223,6 +224,11 @@ class B200LlmExecutor:
     def GetCurrentStep(self) -> int:
         v = C.c_int32()
         _call("B200Lm_GetCurrentStep", self._h, C.byref(v))
+        return v.value
+
+    def GetDecodeMode(self) -> int:
+        v = C.c_int32(0)
+        _call("B200Lm_GetDecodeMode", self._h, C.byref(v))
         return v.value
 
     def GetMaxNumTokens(self) -> int:

@@ -41,6 +41,18 @@ struct LayerWeights {
   float attn_bound;                    // |q.k| / sqrt(hd) <= attn_bound after QK-RMSNorm: sqrt(hd) max|g_q| max|g_k|
 };
 
+// Copies of a layer's decode weights in the layouts the chained kernel streams with ONE bulk copy per
+// ring slot (the barrier-per-phase kernels use the plain tile order of LayerWeights).
+struct ChainedLayer {
+  const unsigned char* wqkv_s;   // per 16-row tile: its KT 512-byte tiles, then its 16 scales (64 bytes)
+  const unsigned char* wgu_s;    // same for the gate / up tiles (alternating)
+  const uint4* wdown_k;          // tiles ordered [k_tile][row_tile]: a 64-feature K slice is contiguous
+  const uint4* wo_s;             // tiles ordered [head slice][row_tile][k_tile of the slice]
+  const float* gA;               // [g_pre_attn | g_post_ffn of the previous layer]
+  const float* gD;               // [g_pre_ffn | g_post_attn]
+  const float* qk;               // [g_q | g_k]
+};
+
 struct LayerKv {
   void* k;               // [pages][hkv][kPage][hd], fp32 or bf16
   void* v;
@@ -56,6 +68,7 @@ struct DecodeState {          // lives in device memory, one per executor
   int err;                    // DeviceError
   unsigned int barrier;       // grid barrier counter (persistent kernel)
   int steps_done;
+  int gave_up[4];             // first bounded wait that gave up: phase code, layer, CTA, kind of wait (chained kernel)
 };
 
 struct DecodeArgs {
@@ -88,6 +101,12 @@ struct DecodeArgs {
   int* step_tokens;     // [capacity][ncols] arg-max of every step since steps_done was reset
   int step_capacity;
   int advance;          // 1: feed arg-max back as next token and bump pos (device loop)
+  // chained kernel only
+  const ChainedLayer* chained;        // device array [n_layers]
+  const unsigned char* head_ws;       // tied embedding as row-tile records (tiles + scales)
+  const float* gH;                    // [g_final | g_post_ffn of the last layer]
+  const float* rope_cs[2];            // [max_ctx][cos(hd/2) | sin(hd/2)]; 0 local, 1 global
+  int* progress;                      // [n_cta] phase code * 1000 + layer each CTA has reached (diagnostics)
   long long* trace;     // optional [n_barriers][n_cta][2] SM-clock stamps (arrive, release), or null
   long long* trace_pts; // optional [n_barriers][n_cta][8] stamps inside the phase that ends at that barrier
 };

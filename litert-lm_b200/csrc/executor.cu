@@ -17,6 +17,7 @@
 #include "common.cuh"
 #include "decode_ops.cuh"
 #include "decode_stream.cuh"
+#include "decode_fused.cuh"
 #include "model_host.h"
 #include "prefill_ops.cuh"
 #include "prefill_gemm_ts.cuh"
@@ -50,6 +51,49 @@ static const uint4* upload_w4t(Model& m, const uint8_t* packed, int64_t rows, in
   std::vector<uint32_t> buf((size_t)rows * K / 8);
   repack_w4t(packed, rows, K, [](int64_t r) { return r; }, buf.data());
   return reinterpret_cast<const uint4*>(upload(m, buf.data(), buf.size()));
+}
+
+// Host-side W4T tiles of a matrix.
+template <typename RowMap>
+static std::vector<uint32_t> w4t_host(const uint8_t* packed, int64_t rows, int64_t K, RowMap map) {
+  std::vector<uint32_t> buf((size_t)rows * K / 8);
+  repack_w4t(packed, rows, K, map, buf.data());
+  return buf;
+}
+// Row-tile records: the KT tiles of a 16-row tile followed by its 16 scales.
+static const unsigned char* upload_w4ts(Model& m, const std::vector<uint32_t>& w4t, const float* scale_tile_order, int64_t rows,
+                                        int64_t K) {
+  const int64_t RT = rows / 16, KT = K / 64, rec = KT * 512 + 64;
+  std::vector<unsigned char> out((size_t)RT * rec);
+  const unsigned char* src = reinterpret_cast<const unsigned char*>(w4t.data());
+  for (int64_t rt = 0; rt < RT; ++rt) {
+    memcpy(out.data() + rt * rec, src + rt * KT * 512, (size_t)KT * 512);
+    memcpy(out.data() + rt * rec + KT * 512, scale_tile_order + rt * 16, 64);
+  }
+  return upload(m, out.data(), out.size());
+}
+// Tiles reordered [k_tile][row_tile].
+static const uint4* upload_w4t_kmajor(Model& m, const std::vector<uint32_t>& w4t, int64_t rows, int64_t K) {
+  const int64_t RT = rows / 16, KT = K / 64;
+  std::vector<uint32_t> out(w4t.size());
+  for (int64_t rt = 0; rt < RT; ++rt)
+    for (int64_t kt = 0; kt < KT; ++kt) memcpy(out.data() + (kt * RT + rt) * 128, w4t.data() + (rt * KT + kt) * 128, 512);
+  return reinterpret_cast<const uint4*>(upload(m, out.data(), out.size()));
+}
+// Tiles reordered [k slice][row_tile][k_tile within the slice].
+static const uint4* upload_w4t_sliced(Model& m, const std::vector<uint32_t>& w4t, int64_t rows, int64_t K, int slices) {
+  const int64_t RT = rows / 16, KT = K / 64, ktc = KT / slices;
+  std::vector<uint32_t> out(w4t.size());
+  for (int64_t sl = 0; sl < slices; ++sl)
+    for (int64_t rt = 0; rt < RT; ++rt)
+      memcpy(out.data() + ((sl * RT + rt) * ktc) * 128, w4t.data() + (rt * KT + sl * ktc) * 128, (size_t)ktc * 512);
+  return reinterpret_cast<const uint4*>(upload(m, out.data(), out.size()));
+}
+static const float* upload_pair(Model& m, const float* a, const float* b, size_t n) {
+  std::vector<float> v(2 * n, 0.f);
+  memcpy(v.data(), a, n * 4);
+  if (b) memcpy(v.data() + n, b, n * 4);
+  return upload(m, v.data(), v.size());
 }
 
 // W4G with rows padded to 128; scales padded with 1.0.
@@ -88,7 +132,14 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
     const TensorEntry& e = qmat("embed", d.vocab, d.d);
     m->embed_rows = upload(*m, bytes(e), (size_t)e.nbytes);
     m->embed_scale = fvec("embed.scale", d.vocab);
-    m->head_w = upload_w4t(*m, bytes(e), d.vocab, d.d);
+    auto ht = w4t_host(bytes(e), d.vocab, d.d, [](int64_t r) { return r; });
+    m->head_w = reinterpret_cast<const uint4*>(upload(*m, ht.data(), ht.size()));
+    m->head_ws = upload_w4ts(*m, ht, reinterpret_cast<const float*>(bytes(rec.need("embed.scale", 1))), d.vocab, d.d);
+  }
+  {
+    int hps = 1;
+    while ((hps * d.hd) % 64 != 0) ++hps;
+    m->o_slices = d.hq % hps == 0 ? d.hq / hps : 1;
   }
   m->g_final = fvec("final_norm", d.d);
   {
@@ -98,6 +149,8 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
   }
   m->layers_host.resize(d.n_layers);
   m->gemm_host.resize(d.n_layers);
+  m->chained_host.resize(d.n_layers);
+  auto fptr = [&](const std::string& nm) { return reinterpret_cast<const float*>(bytes(rec.need(nm, 1))); };
   for (int i = 0; i < d.n_layers; ++i) {
     std::string p = "L" + std::to_string(i) + ".";
     LayerWeights& L = m->layers_host[i];
@@ -114,12 +167,30 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
     const float* sg = reinterpret_cast<const float*>(bytes(rec.need(p + "wgate.scale", 1)));
     const float* su = reinterpret_cast<const float*>(bytes(rec.need(p + "wup.scale", 1)));
     const float* sd = reinterpret_cast<const float*>(bytes(rec.need(p + "wdown.scale", 1)));
-    L.wqkv = upload_w4t(*m, bytes(eqkv), d.nqkv(), d.d);
+    ChainedLayer& Cl = m->chained_host[i];
+    memset(&Cl, 0, sizeof Cl);
+    auto ident = [](int64_t r) { return r; };
+    {
+      auto t = w4t_host(bytes(eqkv), d.nqkv(), d.d, ident);
+      L.wqkv = reinterpret_cast<const uint4*>(upload(*m, t.data(), t.size()));
+      Cl.wqkv_s = upload_w4ts(*m, t, sqkv, d.nqkv(), d.d);
+    }
     L.sqkv = upload(*m, sqkv, d.nqkv());
-    L.wo = upload_w4t(*m, bytes(eo), d.d, d.nq());
+    {
+      auto t = w4t_host(bytes(eo), d.d, d.nq(), ident);
+      L.wo = reinterpret_cast<const uint4*>(upload(*m, t.data(), t.size()));
+      Cl.wo_s = upload_w4t_sliced(*m, t, d.d, d.nq(), m->o_slices);
+    }
     L.so = upload(*m, so, d.d);
-    L.wdown = upload_w4t(*m, bytes(ed), d.d, d.ffn);
+    {
+      auto t = w4t_host(bytes(ed), d.d, d.ffn, ident);
+      L.wdown = reinterpret_cast<const uint4*>(upload(*m, t.data(), t.size()));
+      Cl.wdown_k = upload_w4t_kmajor(*m, t, d.d, d.ffn);
+    }
     L.sdown = upload(*m, sd, d.d);
+    Cl.gA = upload_pair(*m, fptr(p + "pre_attn"), i > 0 ? fptr("L" + std::to_string(i - 1) + ".post_ffn") : nullptr, d.d);
+    Cl.gD = upload_pair(*m, fptr(p + "pre_ffn"), fptr(p + "post_attn"), d.d);
+    Cl.qk = upload_pair(*m, fptr(p + "q_norm"), fptr(p + "k_norm"), d.hd);
     // gate and up share one matrix: canonical rows [gate ; up]
     std::vector<uint8_t> gu((size_t)2 * d.ffn * d.d / 2);
     memcpy(gu.data(), bytes(eg), (size_t)eg.nbytes);
@@ -139,6 +210,7 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
         sc[r] = src < ffn ? sg[src] : su[src - ffn];
       }
       L.sgu = upload(*m, sc.data(), sc.size());
+      Cl.wgu_s = upload_w4ts(*m, buf, sc.data(), 2 * ffn, d.d);
     }
     auto gmax = [&](const std::string& nm) {
       const float* g = reinterpret_cast<const float*>(bytes(rec.need(nm, 1)));
@@ -186,11 +258,20 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
   }
   m->has_tc = want_tc;
   m->layers_dev = upload(*m, m->layers_host.data(), m->layers_host.size());
+  m->chained_dev = upload(*m, m->chained_host.data(), m->chained_host.size());
+  m->gH = upload_pair(*m, fptr("final_norm"), fptr("L" + std::to_string(d.n_layers - 1) + ".post_ffn"), d.d);
   for (int t = 0; t < 2; ++t) {
     std::vector<float> c, s;
     build_rope_table(t ? d.rope_global : d.rope_local, d.hd, d.max_ctx, c, s);
     m->rope_cos[t] = upload(*m, c.data(), c.size());
     m->rope_sin[t] = upload(*m, s.data(), s.size());
+    const int half = d.hd / 2;
+    std::vector<float> cs((size_t)d.max_ctx * d.hd);
+    for (int pz = 0; pz < d.max_ctx; ++pz) {
+      memcpy(cs.data() + (size_t)pz * d.hd, c.data() + (size_t)pz * half, (size_t)half * 4);
+      memcpy(cs.data() + (size_t)pz * d.hd + half, s.data() + (size_t)pz * half, (size_t)half * 4);
+    }
+    m->rope_cs[t] = upload(*m, cs.data(), cs.size());
   }
   return m;
 }
@@ -341,6 +422,7 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
            "this library is built for sm_100a (B200); device reports sm_" + std::to_string(prop.major) +
                std::to_string(prop.minor));
   e->n_sms = prop.multiProcessorCount;
+  e->smem_optin = (size_t)prop.sharedMemPerBlockOptin;
   if (cfg.stream) {
     e->stream = reinterpret_cast<cudaStream_t>(cfg.stream);
   } else {
@@ -355,7 +437,9 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   B2_CHECK(e->prefill_gemm != B200LM_GEMM_TCGEN05 || model->has_tc, kFailedPrecondition,
            "tensor-core GEMM weights were not loaded for this model");
   B2_CHECK(cfg.page_order == 0 || cfg.page_order == 1, kInvalidArgument, "page_order must be 0 or 1");
-  e->decode_mode = cfg.decode_mode == B200LM_DECODE_AUTO ? B200LM_DECODE_PERSISTENT : cfg.decode_mode;
+  B2_CHECK(cfg.decode_mode >= B200LM_DECODE_AUTO && cfg.decode_mode <= B200LM_DECODE_CHAINED, kInvalidArgument,
+           "decode_mode must be one of B200LM_DECODE_*");
+  e->decode_mode = cfg.decode_mode == B200LM_DECODE_AUTO ? B200LM_DECODE_CHAINED : cfg.decode_mode;
   const int esz = d.kv_dtype == 0 ? 4 : 2;
   // ---- paged KV cache
   e->pages_per_seq = (d.max_ctx + kPage - 1) / kPage;
@@ -425,6 +509,11 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   a.g_final = model->g_final;
   a.gmax_final = model->gmax_final;
   for (int t = 0; t < 2; ++t) { a.rope_cos[t] = model->rope_cos[t]; a.rope_sin[t] = model->rope_sin[t]; }
+  a.chained = model->chained_dev;
+  a.head_ws = model->head_ws;
+  a.gH = model->gH;
+  for (int t = 0; t < 2; ++t) a.rope_cs[t] = model->rope_cs[t];
+  a.progress = reinterpret_cast<int*>(e->alloc(sizeof(int) * 2 * e->n_sms, true));   // live words, then a snapshot
   a.st = reinterpret_cast<DecodeState*>(e->alloc(sizeof(DecodeState), true));
   const int G = d.group();
   const int max_splits = std::max(a.n_attn_splits_local, a.n_attn_splits_global);
@@ -443,11 +532,31 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   a.step_tokens = reinterpret_cast<int*>(e->alloc(sizeof(int) * a.step_capacity * kMaxCols, true));
   a.advance = 1;
   // the one-kernel-per-phase fallback drives one session; the persistent kernels carry all of them
-  e->dec_smem = dec_smem_bytes(d, e->decode_mode == B200LM_DECODE_PERSISTENT ? 1 : e->n_sessions);
+  e->dec_smem = dec_smem_bytes(d, (e->decode_mode == B200LM_DECODE_PERSISTENT || e->decode_mode == B200LM_DECODE_CHAINED) ? 1 : e->n_sessions);
   B2_CHECK(e->dec_smem <= (size_t)prop.sharedMemPerBlockOptin, kUnimplemented,
            "decode kernels need more shared memory than the device offers");
   raise_dyn_smem(decode_phase_kernel, (size_t)(e->dec_smem));
   raise_dyn_smem(decode_persistent_kernel, (size_t)(e->dec_smem));
+  if (e->decode_mode == B200LM_DECODE_CHAINED) {
+    // the chained kernel needs its ring to fit and the softmax shift of its attention to be usable;
+    // otherwise the barrier-per-phase streaming kernel takes over
+    FusedPlan pl;
+    size_t smem = 0;
+    const int nc = e->n_sessions, nt = nc * 3 <= kQCols ? 3 : kQCols / nc;
+    const int cap = std::max(1, e->n_sms / (nc * d.hkv));
+    bool ok = prop.cooperativeLaunch &&
+              fused_make_plan(d, nc, nt, e->n_sms, a.o_slices, std::min(a.n_attn_splits_local, cap),
+                              std::min(a.n_attn_splits_global, cap), (size_t)prop.sharedMemPerBlockOptin, &pl, &smem);
+    for (float b : model->attn_bound) ok = ok && b <= kFaMaxBound;
+    ok = ok && a.o_slices == model->o_slices;      // the sliced W_o copy was laid out for this split
+    if (ok) {
+      e->chained_ok = true;
+      e->ll_bytes = (size_t)2 * pl.ll_words * sizeof(fu_u64);
+      e->ll_dev = reinterpret_cast<fu_u64*>(e->alloc(e->ll_bytes, true));
+    } else {
+      e->decode_mode = B200LM_DECODE_PERSISTENT;
+    }
+  }
   if (e->decode_mode == B200LM_DECODE_PERSISTENT) {
     // staging halves take what shared memory the activation staging leaves, up to 96 KiB each
     size_t fixed = stream_fixed_bytes(d, e->n_sessions);
@@ -531,17 +640,34 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
 
 void Executor::check_device_error(const char* where) {
   int err = 0;
-  B2_CUDA(cudaMemcpyAsync(&pin_state->err, &dargs.st->err, sizeof(int), cudaMemcpyDeviceToHost, stream));
+  // err, barrier, steps_done and gave_up[4] are adjacent
+  const size_t tail = sizeof(DecodeState) - offsetof(DecodeState, err);
+  B2_CUDA(cudaMemcpyAsync(&pin_state->err, &dargs.st->err, tail, cudaMemcpyDeviceToHost, stream));
   B2_CUDA(cudaStreamSynchronize(stream));
   err = pin_state->err;
   if (err == kDevOk) return;
-  // clear the word and the barrier count so the handle stays usable
-  B2_CUDA(cudaMemsetAsync(&dargs.st->err, 0, sizeof(int), stream));
-  B2_CUDA(cudaMemsetAsync(&dargs.st->barrier, 0, sizeof(unsigned), stream));
+  // clear the words and the barrier count so the handle stays usable
+  B2_CUDA(cudaMemsetAsync(&dargs.st->err, 0, tail, stream));
   B2_CUDA(cudaStreamSynchronize(stream));
   barrier_epoch = 0;
   std::string w(where);
-  if (err == kDevBarrierTimeout) throw Error{kDeadlineExceeded, w + ": a bounded device-side wait gave up"};
+  if (err == kDevBarrierTimeout) {
+    std::string detail;
+    const int* g = pin_state->gave_up;
+    if (g[3] != 0)
+      detail = " (first: " + std::string(g[3] == 1 ? "poll" : g[3] == 2 ? "ring slot" : "copy producer") + ", phase code " +
+               std::to_string(g[0]) + ", layer / fill " + std::to_string(g[1]) + ", CTA " + std::to_string(g[2]) + ")";
+    if (decode_mode == B200LM_DECODE_CHAINED) {
+      std::vector<int> prog(n_sms);      // the snapshot taken by the first wait that gave up
+      B2_CUDA(cudaMemcpy(prog.data(), dargs.progress + n_sms, sizeof(int) * n_sms, cudaMemcpyDeviceToHost));
+      int lo = 0;
+      for (int i = 1; i < n_sms; ++i)
+        if (prog[i] < prog[lo]) lo = i;
+      detail += "; least advanced CTA " + std::to_string(lo) + " at phase code " + std::to_string(prog[lo] / 1000 % 10) + ", layer " +
+                std::to_string(prog[lo] % 1000) + ", step " + std::to_string(prog[lo] / 10000);
+    }
+    throw Error{kDeadlineExceeded, w + ": a bounded device-side wait gave up" + detail};
+  }
   if (err == kDevBadToken) throw Error{kInvalidArgument, w + ": token id outside the vocabulary"};
   if (err == kDevBadPosition) throw Error{kInvalidArgument, w + ": position outside the KV capacity"};
   throw Error{kInternal, w + ": device error word " + std::to_string(err)};
@@ -725,6 +851,47 @@ void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
   const ModelDims& d = model->dims;
   const int ncta = n_sms;
   if (first_session < 0) first_session = active;
+  if (decode_mode == B200LM_DECODE_CHAINED) {
+    DecodeArgs a = dargs;
+    a.ncols = ncols;
+    a.nterms = ncols * 3 <= kQCols ? 3 : kQCols / ncols;
+    a.page_table = page_table_dev + (size_t)first_session * pages_per_seq;
+    const int cap = std::max(1, ncta / (ncols * d.hkv));
+    a.n_attn_splits_local = std::min(a.n_attn_splits_local, cap);
+    a.n_attn_splits_global = std::min(a.n_attn_splits_global, cap);
+    FusedPlan pl;
+    size_t smem = 0;
+    B2_CHECK(fused_make_plan(d, a.ncols, a.nterms, ncta, a.o_slices, a.n_attn_splits_local, a.n_attn_splits_global,
+                             smem_optin, &pl, &smem),
+             kInternal, "the chained decode kernel does not fit this launch");
+    B2_CHECK((size_t)2 * pl.ll_words * sizeof(fu_u64) <= ll_bytes, kInternal, "exchange area too small");
+    // tags grow by one per (step, layer) and once more per step; start over (area cleared) long before they wrap
+    const unsigned need = (unsigned)nsteps * (unsigned)(d.n_layers + 1) + 2u;
+    if (ll_tag > 0xF0000000u - need) {
+      B2_CUDA(cudaMemsetAsync(ll_dev, 0, ll_bytes, stream));
+      ll_tag = 0;
+    }
+    pl.tag0 = ll_tag;
+    ll_tag += need;
+    const void* kfn = decode_fused_kernel_for(d);
+    raise_dyn_smem(kfn, smem);
+    fu_u64* ll = ll_dev;
+    void* params[] = {&a, &pl, &ll, &nsteps};
+    cudaError_t le = cudaLaunchCooperativeKernel(kfn, dim3(ncta), dim3(kFuThreads), params, smem, stream);
+    if (le != cudaSuccess) {
+      cudaGetLastError();
+      cudaFuncAttributes fa{};
+      cudaFuncGetAttributes(&fa, kfn);
+      int occ = -1;
+      cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kfn, kFuThreads, smem);
+      throw Error{kInternal, std::string("chained decode kernel launch: ") + cudaGetErrorString(le) + " (registers " +
+                                 std::to_string(fa.numRegs) + ", static shared " + std::to_string(fa.sharedSizeBytes) +
+                                 ", dynamic shared " + std::to_string(smem) + ", max threads " +
+                                 std::to_string(fa.maxThreadsPerBlock) + ", blocks per SM " + std::to_string(occ) + ")"};
+    }
+    launches += 1;
+    return;
+  }
   if (decode_mode == B200LM_DECODE_PERSISTENT || decode_mode == B200LM_DECODE_PERSISTENT_BASIC) {
     DecodeArgs a = dargs;
     a.ncols = ncols;
@@ -867,7 +1034,8 @@ void Executor::decode_tokens_batch(int nsteps, int* out_ids) {
 void Executor::trace_decode_step(int* out_id, long long* stamps, long long capacity, int* n_barriers, int* n_cta,
                                  int* khz) {
   const ModelDims& d = model->dims;
-  B2_CHECK(decode_mode == B200LM_DECODE_PERSISTENT || decode_mode == B200LM_DECODE_PERSISTENT_BASIC,
+  B2_CHECK(decode_mode == B200LM_DECODE_PERSISTENT || decode_mode == B200LM_DECODE_PERSISTENT_BASIC ||
+               decode_mode == B200LM_DECODE_CHAINED,
            kFailedPrecondition, "the decode timeline needs a persistent decode mode");
   B2_CUDA(cudaSetDevice(device));
   const int nb = 5 * d.n_layers + 2;
@@ -1115,6 +1283,13 @@ int B200Lm_GetMaxNumTokens(B200LmExecutor* e, int32_t* out, char** err) {
   B2_API_BEGIN
   B2_CHECK(e && e->impl && out, kInvalidArgument, "null argument");
   *out = e->impl->max_num_tokens;
+  B2_API_END
+}
+
+int B200Lm_GetDecodeMode(B200LmExecutor* e, int32_t* out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && out, kInvalidArgument, "null argument");
+  *out = e->impl->decode_mode;
   B2_API_END
 }
 

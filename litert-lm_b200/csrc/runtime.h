@@ -10,6 +10,7 @@
 #include "../../include/b200lm.h"
 #include "common.cuh"
 #include "decode_ops.cuh"
+#include "decode_fused.cuh"
 
 namespace b200lm {
 
@@ -36,6 +37,13 @@ struct Model {
   std::vector<LayerGemmWeights> gemm_host;
   std::vector<float> attn_bound;     // per layer: sqrt(hd) max|g_q| max|g_k| >= any |q.k| / sqrt(hd)
   const LayerWeights* layers_dev = nullptr;
+  // layouts of the chained decode kernel (see ChainedLayer)
+  int o_slices = 1;                  // head slices of the o-proj (K split by whole heads, 64-wide at least)
+  std::vector<ChainedLayer> chained_host;
+  const ChainedLayer* chained_dev = nullptr;
+  const unsigned char* head_ws = nullptr;
+  const float* gH = nullptr;
+  const float* rope_cs[2] = {nullptr, nullptr};
   std::vector<void*> allocations;
 
   ~Model();
@@ -69,6 +77,7 @@ class Executor {
   std::shared_ptr<Model> model;
   int device = 0;
   int n_sms = 0;
+  size_t smem_optin = 0;            // opt-in shared memory per block of the device
   cudaStream_t stream = nullptr;
   bool own_stream = false;
   int max_num_tokens = 0;
@@ -108,6 +117,11 @@ class Executor {
   size_t stream_smem = 0;
   int stream_half = 0;
   unsigned barrier_epoch = 0;
+  // chained decode kernel: exchange area (two parity copies of flag-carrying words) and the next free tag
+  fu_u64* ll_dev = nullptr;
+  size_t ll_bytes = 0;
+  unsigned ll_tag = 0;
+  bool chained_ok = false;          // the model fits the chained kernel (with n_sessions columns)
   long long* trace_dev = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
   // prefill scratch

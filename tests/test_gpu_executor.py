@@ -31,6 +31,7 @@ def run_pair(pkg, orc, models, name, prompt, steps, **kw):
 @pytest.mark.parametrize("name,prompt_len,mode,gemm", [
     ("tiny", 32, 1, 1), ("tiny", 32, 2, 1), ("tiny", 32, 2, 2), ("tiny", 32, 3, 2), ("small", 200, 1, 1),
     ("small", 200, 2, 2), ("small", 300, 2, 2), ("small", 300, 3, 1), ("small-gqa", 150, 2, 2), ("small-gqa", 150, 1, 1),
+    ("tiny", 32, 4, 1), ("small", 200, 4, 2), ("small", 300, 4, 1), ("small-gqa", 150, 4, 2),
 ])
 def test_logits_and_greedy_tokens_match_oracle(pkg, orc, models, name, prompt_len, mode, gemm):
     """Teacher-forced on the oracle's token every step, so one flip cannot hide later errors."""
@@ -219,7 +220,7 @@ def test_greedy_ties_pick_the_lowest_index(pkg, orc, mio):
     ref = orc.OracleExecutor(orc.OracleModel(rec))
     assert ref.prefill(prompt) == 0
     want = [ref.decode_token()[1] for _ in range(16)]
-    for mode in (2, 1):
+    for mode in (4, 2, 1):
         ex = pkg.B200LlmExecutor(img, decode_mode=mode)
         ex.Prefill(prompt)
         got = list(ex.DecodeTokens(16))
@@ -227,3 +228,12 @@ def test_greedy_ties_pick_the_lowest_index(pkg, orc, mio):
     tied = [t for t in want if any(t in g for g in groups)]
     assert tied, "no planted row won a step: the case does not exercise ties"
     assert all(t == g[0] for t in tied for g in groups if t in g)     # always the lowest member
+
+
+@pytest.mark.parametrize("name", ["tiny", "small", "small-gqa"])
+def test_auto_decode_mode_is_the_chained_kernel(pkg, models, name):
+    """AUTO must resolve to the barrier-free chained kernel on every test shape (a silent
+    fall-back to the slower kernels would still pass the parity tests)."""
+    cfg, rec, img = models(name)
+    assert pkg.B200LlmExecutor(img).GetDecodeMode() == pkg.DECODE_CHAINED
+    assert pkg.B200LlmExecutor(img, decode_mode=pkg.DECODE_PERSISTENT).GetDecodeMode() == pkg.DECODE_PERSISTENT
