@@ -214,11 +214,10 @@ __host__ inline bool fused_make_plan(const ModelDims& d, int ncols, int nterms, 
   const int KTd = d.ffn / 64;
   pl.ffn_m = (KTd + ncta - 1) / ncta;
   pl.nprod = (KTd + pl.ffn_m - 1) / pl.ffn_m;
-  pl.d_tps = pl.slot_bytes / (pl.ffn_m * 512);
+  pl.d_tps = pl.slot_bytes / (pl.ffn_m * 512 + 64);     // row tiles of the K slice with their 16 scales each
   if (pl.d_tps < 1) return false;
   pl.d_tps = fu_pow2_floor(pl.d_tps);
   if (pl.d_tps > 64) pl.d_tps = 64;
-  if (pl.slot_bytes < d.d * 4) return false;                                                   // down-projection scales
   pl.r_per = fu_round_up((d.d + ncta - 1) / ncta, 4);
   pl.nred = (d.d + pl.r_per - 1) / pl.r_per;
   pl.kps = fu_pow2_floor(pl.slot_bytes / (2 * d.hd * esz));
@@ -342,19 +341,17 @@ __device__ __forceinline__ bool fu_spin_check(FusedCtx& c, long& spins) {
 // Two values at p (16-byte aligned) once both carry `tag`.
 __device__ __forceinline__ float2 ll_wait2(FusedCtx& c, const fu_u64* p, unsigned tag) {
   fu_u64 w0 = 0, w1 = 0;
-  if (!*c.dead) {
-    long spins = 0;
-    while (true) {
-      ll_load2(p, w0, w1);
-      if (ll_ok(w0, tag) && ll_ok(w1, tag)) break;
-      if (!fu_spin_check(c, spins)) break;
-    }
+  long spins = 0;
+  while (true) {
+    ll_load2(p, w0, w1);
+    if (ll_ok(w0, tag) && ll_ok(w1, tag)) break;
+    if (!fu_spin_check(c, spins)) break;
   }
   return make_float2(ll_val(w0), ll_val(w1));
 }
 __device__ __forceinline__ fu_u64 ll_wait1(FusedCtx& c, const fu_u64* p, unsigned tag) {
   fu_u64 w = 0;
-  if (!*c.dead) {
+  {
     long spins = 0;
     while (true) {
       w = ll_load1(p);
@@ -367,7 +364,7 @@ __device__ __forceinline__ fu_u64 ll_wait1(FusedCtx& c, const fu_u64* p, unsigne
 // Four values at p (32-byte aligned): both 16-byte loads are in flight together.
 __device__ __forceinline__ float4 ll_wait4(FusedCtx& c, const fu_u64* p, unsigned tag) {
   fu_u64 w0 = 0, w1 = 0, w2 = 0, w3 = 0;
-  if (!*c.dead) {
+  {
     long spins = 0;
     while (true) {
       ll_load2(p, w0, w1);
@@ -411,6 +408,19 @@ __device__ __forceinline__ void fu_quantize4(float4 r, int nterms, int8_t* row0,
 
 // ------------------------------------------------------------------ int4 x int8 tiles
 
+// mma.sync m16n8k32 s8 x s8 -> s32 as a pure function of its operands (no volatile: the compiler may
+// interleave the chains of several tiles).
+__device__ __forceinline__ void fu_mma_s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm("mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void fu_mma_tile(int (&acc)[4], const uint4& w, const uint4& b) {
+  const uint32_t m = 0xF0F0F0F0u;   // high nibble of every byte = 16 * q as int8
+  fu_mma_s8(acc, (w.x << 4) & m, w.x & m, (w.y << 4) & m, w.y & m, b.x, b.y);
+  fu_mma_s8(acc, (w.z << 4) & m, w.z & m, (w.w << 4) & m, w.w & m, b.z, b.w);
+}
+
 // Tile blocks [kt0, kt1) of one 16-row tile (block kt at wt + kt * kstride) against the quantised columns.
 // Two accumulator chains (even / odd k tiles) hide the MMA latency.
 __device__ __forceinline__ int4 fu_mma_run(const uint4* wt, int kstride, int kt0, int kt1, const int8_t* xq, int xstride, int nq,
@@ -424,13 +434,13 @@ __device__ __forceinline__ int4 fu_mma_run(const uint4* wt, int kstride, int kt0
   for (; kt + 1 < kt1; kt += 2) {
     const uint4 w0 = wt[(size_t)kt * kstride + lane], w1 = wt[(size_t)(kt + 1) * kstride + lane];
     const uint4 b0 = ok ? bp[kt * 4] : zero, b1 = ok ? bp[(kt + 1) * 4] : zero;
-    mma_tile_words(a0, w0, b0.x, b0.y, b0.z, b0.w);
-    mma_tile_words(a1, w1, b1.x, b1.y, b1.z, b1.w);
+    fu_mma_tile(a0, w0, b0);
+    fu_mma_tile(a1, w1, b1);
   }
   if (kt < kt1) {
     const uint4 w0 = wt[(size_t)kt * kstride + lane];
     const uint4 b0 = ok ? bp[kt * 4] : zero;
-    mma_tile_words(a0, w0, b0.x, b0.y, b0.z, b0.w);
+    fu_mma_tile(a0, w0, b0);
   }
   return make_int4(a0[0] + a1[0], a0[1] + a1[1], a0[2] + a1[2], a0[3] + a1[3]);
 }
@@ -609,7 +619,7 @@ __device__ __forceinline__ float4 ll_sum4_parts(FusedCtx& c, const fu_u64* p, si
     fu_u64 w[4][4];
 #pragma unroll
     for (int q = 0; q < 4; ++q) w[q][0] = w[q][1] = w[q][2] = w[q][3] = 0;
-    if (!*c.dead) {
+    {
       long spins = 0;
       while (true) {
         bool ok = true;
@@ -623,7 +633,20 @@ __device__ __forceinline__ float4 ll_sum4_parts(FusedCtx& c, const fu_u64* p, si
           }
         }
         if (ok) break;
-        if (!fu_spin_check(c, spins)) break;
+        if (!fu_spin_check(c, spins)) {
+          if (c.gave_up[2] == (int)blockIdx.x && atomicCAS(c.gave_up + 7, 0, (int)threadIdx.x + 1) == 0) {
+            int bad = 0;
+            for (int q = 0; q < 4; ++q)
+              for (int e = 0; e < 4; ++e)
+                if (q < nb && !ll_ok(w[q][e], tag) && bad == 0) {
+                  bad = 1;
+                  c.gave_up[4] = (int)(unsigned)(w[q][e] >> 32);
+                  c.gave_up[5] = (int)tag;
+                  c.gave_up[6] = (int)((p + (size_t)(p0 + q) * stride + e) - c.ll_base);
+                }
+          }
+          break;
+        }
       }
     }
 #pragma unroll
@@ -644,7 +667,7 @@ __device__ __forceinline__ float2 ll_sum2_strided(FusedCtx& c, const fu_u64* p, 
     fu_u64 w[4][2];
 #pragma unroll
     for (int q = 0; q < 4; ++q) w[q][0] = w[q][1] = 0;
-    if (!*c.dead) {
+    {
       long spins = 0;
       while (true) {
         bool ok = true;
@@ -670,7 +693,7 @@ __device__ __forceinline__ float2 ll_sum2_strided(FusedCtx& c, const fu_u64* p, 
 
 __device__ __forceinline__ ulonglong2 ll_wait2w(FusedCtx& c, const fu_u64* p, unsigned tag) {
   fu_u64 w0 = 0, w1 = 0;
-  if (!*c.dead) {
+  {
     long spins = 0;
     while (true) {
       ll_load2(p, w0, w1);
@@ -1185,30 +1208,36 @@ __device__ __forceinline__ FusedCta fu_cta_share(const DecodeArgs& a, const Fuse
 
 // ------------------------------------------------------------------ producer warp
 
-// Waits for the slot of fill n to be free and arms its barrier for `bytes`; returns the slot, or nullptr
-// when the wait gave up (the CTA is then marked dead).
-__device__ __noinline__ unsigned char* fu_prod_begin(FusedCtx& c, unsigned n, uint32_t bytes) {
+// The slot of fill n is still in use: bounded wait.  False when it gave up (the CTA is then marked dead).
+__device__ __noinline__ bool fu_prod_wait_slow(FusedCtx& c, unsigned n) {
+  if (*c.dead) return false;
   const unsigned s = n & (unsigned)(c.nslots - 1);
-  if (n >= (unsigned)c.nslots) {
-    if (*c.dead) return nullptr;
-    if (!mbar_wait(&c.empty[s], ((n >> c.nslots_log2) - 1u) & 1u, c.err)) {
-      if ((threadIdx.x & 31) == 0 && atomicCAS(c.gave_up + 3, 0, 3) == 0) {
-        c.gave_up[0] = 8;
-        c.gave_up[1] = (int)n;
-        c.gave_up[2] = blockIdx.x;
-      }
-      *c.dead = 1;
-      return nullptr;
+  if (!mbar_wait(&c.empty[s], ((n >> c.nslots_log2) - 1u) & 1u, c.err)) {
+    if ((threadIdx.x & 31) == 0 && atomicCAS(c.gave_up + 3, 0, 3) == 0) {
+      c.gave_up[0] = 8;
+      c.gave_up[1] = (int)n;
+      c.gave_up[2] = blockIdx.x;
     }
+    *c.dead = 1;
+    return false;
+  }
+  return true;
+}
+// Waits for the slot of fill n to be free and arms its barrier for `bytes`; returns the slot, or nullptr
+// when the wait gave up.
+__device__ __forceinline__ unsigned char* fu_prod_begin(const FusedRing& r, FusedCtx& c, unsigned n, uint32_t bytes) {
+  const unsigned s = n & r.mask;
+  if (n > r.mask && !mbar_test(&r.empty[s], ((n >> r.log2) - 1u) & 1u)) {
+    if (!fu_prod_wait_slow(c, n)) return nullptr;
   }
   if ((threadIdx.x & 31) == 0) {
-    mbar_arrive_expect_tx(&c.full[s], bytes);
+    mbar_arrive_expect_tx(&r.full[s], bytes);
     if (c.fill_log && n < 4000u) c.fill_log[3 * n] = clock64();
   }
   __syncwarp();
-  return c.ring + (size_t)s * c.slot_bytes;
+  return r.ring + (size_t)s * r.slot_bytes;
 }
-__device__ __forceinline__ uint64_t* fu_prod_bar(FusedCtx& c, unsigned n) { return &c.full[n & (unsigned)(c.nslots - 1)]; }
+__device__ __forceinline__ uint64_t* fu_prod_bar(const FusedRing& r, unsigned n) { return &r.full[n & r.mask]; }
 
 template <typename T>
 __device__ __noinline__ void fused_producer(const DecodeArgs& a, const FusedPlan& pl, FusedCtx& c, const FusedCta& sh, int nsteps) {
@@ -1216,14 +1245,15 @@ __device__ __noinline__ void fused_producer(const DecodeArgs& a, const FusedPlan
   const int lane = threadIdx.x & 31, cta = blockIdx.x;
   const int ktn = dm.d / 64;
   const uint32_t rec_b = (uint32_t)ktn * 512u + 64u, gain_b = (uint32_t)dm.d * 4u;
+  const FusedRing rg = fu_ring(c);
   unsigned n = 0;                    // next fill
   unsigned char* dst;
 // one contiguous copy fills the slot
 #define FU_FILL1(src, bytes)                                                      \
   do {                                                                            \
-    dst = fu_prod_begin(c, n, (bytes));                                           \
+    dst = fu_prod_begin(rg, c, n, (bytes));                                           \
     if (!dst) return;                                                             \
-    if (lane == 0) bulk_load_1d(dst, (src), (bytes), fu_prod_bar(c, n));          \
+    if (lane == 0) bulk_load_1d(dst, (src), (bytes), fu_prod_bar(rg, n));          \
     ++n;                                                                          \
   } while (0)
   for (int step = 0; step < nsteps; ++step) {
@@ -1246,10 +1276,10 @@ __device__ __noinline__ void fused_producer(const DecodeArgs& a, const FusedPlan
         if (it.item >= 0) {
           const int t = L.is_global ? 1 : 0;
           const uint32_t rope_b = (uint32_t)dm.hd * 4u, qk_b = 2u * (uint32_t)dm.hd * 4u;
-          dst = fu_prod_begin(c, n, rope_b + qk_b);
+          dst = fu_prod_begin(rg, c, n, rope_b + qk_b);
           if (!dst) return;
-          if (lane == 0) bulk_load_1d(dst, a.rope_cs[t] + (size_t)it.pos * dm.hd, rope_b, fu_prod_bar(c, n));
-          if (lane == 1) bulk_load_1d(dst + rope_b, Cl.qk, qk_b, fu_prod_bar(c, n));
+          if (lane == 0) bulk_load_1d(dst, a.rope_cs[t] + (size_t)it.pos * dm.hd, rope_b, fu_prod_bar(rg, n));
+          if (lane == 1) bulk_load_1d(dst + rope_b, Cl.qk, qk_b, fu_prod_bar(rg, n));
           ++n;
           // K rows of a slot's keys, then their V rows; keys of one page are contiguous in the cache
           const uint32_t rowb = (uint32_t)dm.hd * (uint32_t)sizeof(T);
@@ -1258,7 +1288,7 @@ __device__ __noinline__ void fused_producer(const DecodeArgs& a, const FusedPlan
           const unsigned char* vb = reinterpret_cast<const unsigned char*>(c.lkv[layer].v);
           for (int r0 = 0; r0 < it.n_old; r0 += pl.kps) {
             const int nr = min(pl.kps, it.n_old - r0);
-            dst = fu_prod_begin(c, n, 2u * (uint32_t)nr * rowb);
+            dst = fu_prod_begin(rg, c, n, 2u * (uint32_t)nr * rowb);
             if (!dst) return;
             // lanes 0 / 1: K rows before / after a page boundary, lanes 2 / 3: V rows
             if (lane < 4) {
@@ -1270,7 +1300,7 @@ __device__ __noinline__ void fused_producer(const DecodeArgs& a, const FusedPlan
                 const int key = key0 + rbeg;
                 const size_t off = ((((size_t)ptab[key / kPage] * dm.hkv + it.kvh) * kPage + (key % kPage)) * dm.hd) * sizeof(T);
                 bulk_load_1d(dst + (size_t)((isv ? pl.kps : 0) + rbeg) * rowb, (isv ? vb : kb) + off, (uint32_t)rn * rowb,
-                             fu_prod_bar(c, n));
+                             fu_prod_bar(rg, n));
               }
             }
             ++n;
@@ -1283,29 +1313,31 @@ __device__ __noinline__ void fused_producer(const DecodeArgs& a, const FusedPlan
         const uint32_t ctile = (uint32_t)ktc * 512u;
         for (int t0 = 0; t0 < sh.c_n; t0 += pl.c_tps) {
           const int nt = min(pl.c_tps, sh.c_n - t0);
-          dst = fu_prod_begin(c, n, (uint32_t)nt * (ctile + 64u));
+          dst = fu_prod_begin(rg, c, n, (uint32_t)nt * (ctile + 64u));
           if (!dst) return;
           if (lane == 0)
-            bulk_load_1d(dst, Cl.wo_s + (((size_t)sh.c_slice * RT + sh.c_t0 + t0) * ktc) * 32, (uint32_t)nt * ctile, fu_prod_bar(c, n));
+            bulk_load_1d(dst, Cl.wo_s + (((size_t)sh.c_slice * RT + sh.c_t0 + t0) * ktc) * 32, (uint32_t)nt * ctile, fu_prod_bar(rg, n));
           if (lane == 1)
-            bulk_load_1d(dst + (size_t)nt * ctile, L.so + (size_t)(sh.c_t0 + t0) * 16, (uint32_t)nt * 64u, fu_prod_bar(c, n));
+            bulk_load_1d(dst + (size_t)nt * ctile, L.so + (size_t)(sh.c_t0 + t0) * 16, (uint32_t)nt * 64u, fu_prod_bar(rg, n));
           ++n;
         }
       }
-      // ---- DE: gains, gate / up records of this CTA's features, scales of W_down, its K slice of W_down
+      // ---- DE: gains, gate / up records of this CTA's features, its K slice of W_down
       FU_FILL1(Cl.gD, 2u * gain_b);
       if (sh.f_prod >= 0) {
         for (int i = 0; i < 8 * sh.f_mk; ++i) FU_FILL1(Cl.wgu_s + (size_t)(8 * sh.f_kt0 + i) * rec_b, rec_b);
-        FU_FILL1(L.sdown, gain_b);
-        // [k_tile][row_tile] order: a slot holds, for each k tile of the slice, `nt` consecutive row tiles
+        // [k_tile][row_tile] order: a slot holds, for each k tile of the slice, `nt` consecutive row tiles,
+        // then the scales of those rows
         const int nrt = dm.d / 16;
         for (int t0 = 0; t0 < nrt; t0 += pl.d_tps) {
           const int nt = min(pl.d_tps, nrt - t0);
-          dst = fu_prod_begin(c, n, (uint32_t)(nt * sh.f_mk) * 512u);
+          dst = fu_prod_begin(rg, c, n, (uint32_t)(nt * sh.f_mk) * 512u + (uint32_t)nt * 64u);
           if (!dst) return;
           if (lane < sh.f_mk)
             bulk_load_1d(dst + (size_t)lane * nt * 512, Cl.wdown_k + ((size_t)(sh.f_kt0 + lane) * nrt + t0) * 32, (uint32_t)nt * 512u,
-                         fu_prod_bar(c, n));
+                         fu_prod_bar(rg, n));
+          if (lane == 31)
+            bulk_load_1d(dst + (size_t)nt * sh.f_mk * 512, L.sdown + (size_t)t0 * 16, (uint32_t)nt * 64u, fu_prod_bar(rg, n));
           ++n;
         }
       }
@@ -1431,48 +1463,40 @@ __device__ __forceinline__ unsigned fu_ffn_fast(const DecodeArgs& a, const Fused
   }
   dec_sync();
   FU_TP(3);
-  if (warp == 0) {
+  if (warp < 2) {                    // 64 features, one per lane of two warps
     const float cs = c.colscale[0] * (1.0f / 16.0f);
-    float av[2];
+    const int f = threadIdx.x, pp = f >> 4, row = f & 15;
+    float gate = 0.f, up = 0.f;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const int f = lane + 32 * h, pp = f >> 4, row = f & 15;
-      float gate = 0.f, up = 0.f;
-#pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        gate += c.act[((q * 4 + pp) * 2) * 16 + row];
-        up += c.act[((q * 4 + pp) * 2 + 1) * 16 + row];
-      }
-      const float sg = reinterpret_cast<const float*>(fu_slot(rg, fill_no + 2u * pp) + (size_t)ktn * 512)[row];
-      const float su = reinterpret_cast<const float*>(fu_slot(rg, fill_no + 2u * pp + 1u) + (size_t)ktn * 512)[row];
-      av[h] = gelu_tanh(gate * cs * sg) * (up * cs * su);
+    for (int q = 0; q < 4; ++q) {
+      gate += c.act[((q * 4 + pp) * 2) * 16 + row];
+      up += c.act[((q * 4 + pp) * 2 + 1) * 16 + row];
     }
-    const float m = warp_max(fmaxf(fabsf(av[0]), fabsf(av[1])));
-    const float inv = m > 0.f ? 127.0f / m : 0.f;
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-      const float v = av[h] * inv;
-      const float t0 = rintf(v), r1 = (v - t0) * 128.0f, t1 = rintf(r1), t2 = rintf((r1 - t1) * 128.0f);
-      int8_t* q8 = c.xq + fu_perm(lane + 32 * h);
-      q8[0] = (int8_t)(int)t0;
-      q8[c.xstride] = (int8_t)(int)t1;
-      q8[2 * c.xstride] = (int8_t)(int)t2;
-    }
-    if (lane == 0) c.colscale[0] = m > 0.f ? m / 127.0f : 0.f;
+    const float sg = reinterpret_cast<const float*>(fu_slot(rg, fill_no + 2u * pp) + (size_t)ktn * 512)[row];
+    const float su = reinterpret_cast<const float*>(fu_slot(rg, fill_no + 2u * pp + 1u) + (size_t)ktn * 512)[row];
+    const float av = gelu_tanh(gate * cs * sg) * (up * cs * su);
+    float m = warp_max(fabsf(av));
+    if (lane == 0) c.scratch[warp] = m;
+    asm volatile("bar.sync 2, 64;" ::: "memory");       // the two warps only
+    m = fmaxf(c.scratch[0], c.scratch[1]);
+    const float v = av * (m > 0.f ? 127.0f / m : 0.f);
+    const float t0 = rintf(v), r1 = (v - t0) * 128.0f, t1 = rintf(r1), t2 = rintf((r1 - t1) * 128.0f);
+    int8_t* q8 = c.xq + fu_perm(f);
+    q8[0] = (int8_t)(int)t0;
+    q8[c.xstride] = (int8_t)(int)t1;
+    q8[2 * c.xstride] = (int8_t)(int)t2;
+    if (threadIdx.x == 0) c.colscale[0] = m > 0.f ? m / 127.0f : 0.f;
   }
   dec_sync();
   FU_TP(4);
   if (threadIdx.x < 8) mbar_arrive(&rg.empty[(fill_no + threadIdx.x) & mask]);    // gate / up slots
   fill_no += 8;
-  const unsigned sf = fill_no;                           // scales of W_down, then its K slice
-  const int nrt = d / 16, nf = (nrt + pl.d_tps - 1) / pl.d_tps;
-  fu_acquire(rg, c, sf);
-  for (int f = 0; f < nf; ++f) fu_acquire(rg, c, sf + 1 + f);
+  const int nrt = d / 16, nf = (nrt + pl.d_tps - 1) / pl.d_tps;      // the K slice of W_down with its scales
+  for (int f = 0; f < nf; ++f) fu_acquire(rg, c, fill_no + f);
   if (warp == 0) FU_TP(6);
-  fu_gemv_fast(c, sf + 1, fu_log2(pl.d_tps), nrt, 1, reinterpret_cast<const float*>(fu_slot(rg, sf)), true,
-               FusedOut{out, nullptr, d, 0, tag});
-  fu_release(rg, sf, nf + 1);
-  return sf + 1 + nf;
+  fu_gemv_fast(c, fill_no, fu_log2(pl.d_tps), nrt, 1, nullptr, true, FusedOut{out, nullptr, d, 0, tag});
+  fu_release(rg, fill_no, nf);
+  return fill_no + nf;
 }
 
 // DE: residual update + pre-FFN norm -> gate / up rows of this CTA's features -> GeGLU -> its K slice of
@@ -1494,7 +1518,7 @@ __device__ __forceinline__ unsigned fu_phase_ffn(const DecodeArgs& a, const Fuse
   fu_release(rg, gf, 1);
   fill_no = gf + 1;
   const int nf_down = (d / 16 + pl.d_tps - 1) / pl.d_tps;
-  if (sh.f_prod >= 0 && ncols == 1 && a.nterms == 3 && sh.f_mk == 1 && pl.round_fills >= 8 && nf_down + 1 <= pl.round_fills) {
+  if (sh.f_prod >= 0 && ncols == 1 && a.nterms == 3 && sh.f_mk == 1 && pl.round_fills >= 8 && nf_down <= pl.round_fills) {
     fill_no = fu_ffn_fast(a, pl, c, sh, fill_no, ll + pl.ll_fpart + (size_t)sh.f_prod * d, tag, bar);
   } else if (sh.f_prod >= 0) {
     const int ngu = 8 * sh.f_mk, K2 = 64 * sh.f_mk;
@@ -1517,23 +1541,18 @@ __device__ __forceinline__ unsigned fu_phase_ffn(const DecodeArgs& a, const Fuse
     dec_sync();
     fu_quantize_dynamic(a, c, c.act, K2);
     FU_TP(4);
-    const unsigned sf = fill_no;                       // scales of W_down
-    fu_acquire(rg, c, sf);
-    const float* sdown = reinterpret_cast<const float*>(fu_slot(rg, sf));
-    fill_no = sf + 1;
     const int nrt = d / 16, nf_all = (nrt + pl.d_tps - 1) / pl.d_tps;
-    const int rf = pl.round_fills - 1;
+    const int rf = pl.round_fills;
     fu_u64* out = ll + pl.ll_fpart + (size_t)sh.f_prod * ncols * d;
     for (int fr = 0; fr < nf_all; fr += rf) {
       const int nf = min(rf, nf_all - fr);
       const int t0 = fr * pl.d_tps, nt = min(nrt - t0, nf * pl.d_tps);
       for (int f = 0; f < nf; ++f) fu_acquire(rg, c, fill_no + f);
       if (fr == 0) FU_TP(6);
-      fu_gemv_round(c, fill_no, pl.d_tps, nt, sh.f_mk, sdown + t0 * 16, true, ncols, a.nterms, FusedOut{out, nullptr, d, t0 * 16, tag});
+      fu_gemv_round(c, fill_no, pl.d_tps, nt, sh.f_mk, nullptr, true, ncols, a.nterms, FusedOut{out, nullptr, d, t0 * 16, tag});
       fu_release(rg, fill_no, nf);
       fill_no += nf;
     }
-    fu_release(rg, sf, 1);
   }
   FU_ARRIVE();
   return fill_no;
@@ -1607,20 +1626,21 @@ __device__ __forceinline__ unsigned fu_phase_head(const DecodeArgs& a, const Fus
     fu_release(rg, gf, 1);
     const unsigned f0 = gf + 1;
     const int nq = ncols * nterms;
+    const bool timed = a.trace_pts != nullptr;      // the timeline tool asks where the warps spend the phase
     long long t_wait = 0, t_mma = 0, t_fin = 0;
     for (int i = warp; i < sh.h_n; i += kDecWarps) {
       const unsigned fill = f0 + (unsigned)i;
-      long long t0 = clock64();
+      const long long t0 = timed ? clock64() : 0;
       fu_acquire(rg, c, fill);
-      long long t1 = clock64();
+      const long long t1 = timed ? clock64() : 0;
       const unsigned char* base = fu_slot(rg, fill);
       const int4 acc = fu_mma_run(reinterpret_cast<const uint4*>(base), 32, 0, ktn, c.xq, c.xstride, nq, lane);
       const float* scl = reinterpret_cast<const float*>(base + (size_t)ktn * 512);
       const int n0 = (sh.h_t0 + i) * 16;
-      long long t2;
+      long long t2 = 0;
       if (ncols == 1 && nterms == 3) {          // finalised in registers: rows g and g + 8 in the lanes with t == 0
         const float2 v = fu_terms(acc);
-        t2 = clock64();
+        if (timed) t2 = clock64();
         if ((lane & 3) == 0) {
           const int gq = lane >> 2;
           const float cs = c.colscale[0] * (1.0f / 16.0f);
@@ -1633,7 +1653,7 @@ __device__ __forceinline__ unsigned fu_phase_head(const DecodeArgs& a, const Fus
       } else {
         fu_store_frag(c.red, warp, acc, lane);
         __syncwarp();
-        t2 = clock64();
+        if (timed) t2 = clock64();
 #pragma unroll
         for (int k = 0; k < kMaxCols / 2; ++k) {
           const int row = lane & 15, col = (lane >> 4) + 2 * k;
@@ -1648,11 +1668,11 @@ __device__ __forceinline__ unsigned fu_phase_head(const DecodeArgs& a, const Fus
       t_mma += t2 - t1;
       __syncwarp();
       if (lane == 0) mbar_arrive(&rg.empty[fill & rg.mask]);
-      t_fin += clock64() - t2;
+      if (timed) t_fin += clock64() - t2;
     }
     fill_no = f0 + (unsigned)sh.h_n;
     FU_TP(3);
-    if (a.trace_pts && threadIdx.x == 0) {      // development: where warp 0 spent the head phase (cycles)
+    if (timed && threadIdx.x == 0) {                // where warp 0 spent the head phase (cycles)
       long long* q = a.trace_pts + ((size_t)(bar + 1) * gridDim.x + blockIdx.x) * 8;
       q[4] = t_wait; q[5] = t_mma; q[6] = t_fin;
     }

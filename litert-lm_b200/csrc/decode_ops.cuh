@@ -68,7 +68,8 @@ struct DecodeState {          // lives in device memory, one per executor
   int err;                    // DeviceError
   unsigned int barrier;       // grid barrier counter (persistent kernel)
   int steps_done;
-  int gave_up[4];             // first bounded wait that gave up: phase code, layer, CTA, kind of wait (chained kernel)
+  int gave_up[8];             // first bounded wait that gave up (chained kernel): phase code, layer, CTA, kind of wait,
+                              // then for a poll: tag seen, tag wanted, word offset in the exchange area, thread
 };
 
 struct DecodeArgs {

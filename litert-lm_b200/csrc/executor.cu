@@ -656,13 +656,46 @@ void Executor::check_device_error(const char* where) {
     const int* g = pin_state->gave_up;
     if (g[3] != 0)
       detail = " (first: " + std::string(g[3] == 1 ? "poll" : g[3] == 2 ? "ring slot" : "copy producer") + ", phase code " +
-               std::to_string(g[0]) + ", layer / fill " + std::to_string(g[1]) + ", CTA " + std::to_string(g[2]) + ")";
+               std::to_string(g[0]) + ", layer / fill " + std::to_string(g[1]) + ", CTA " + std::to_string(g[2]) +
+               (g[7] ? ", thread " + std::to_string(g[7] - 1) + " saw tag " + std::to_string((unsigned)g[4]) + " for " +
+                           std::to_string((unsigned)g[5]) + " at word " + std::to_string(g[6]) + " (tag0 " +
+                           std::to_string(last_plan_ll.tag0) + ", words per copy " + std::to_string(last_plan_ll.ll_words) +
+                           ", ffn out at " + std::to_string(last_plan_ll.ll_f) + ")"
+                     : std::string()) + ")";
     if (decode_mode == B200LM_DECODE_CHAINED) {
       std::vector<int> prog(n_sms);      // the snapshot taken by the first wait that gave up
       B2_CUDA(cudaMemcpy(prog.data(), dargs.progress + n_sms, sizeof(int) * n_sms, cudaMemcpyDeviceToHost));
+      // a word is step * 10000 + phase code * 1000 + layer; order in time: step, layer, phase (the head phases 6, 7 last)
+      auto when = [&](int w) {
+        const int code = w / 1000 % 10, layer = code >= 6 ? model->dims.n_layers : w % 1000;
+        return (long)(w / 10000) * 1000000L + (long)layer * 10 + code;
+      };
       int lo = 0;
       for (int i = 1; i < n_sms; ++i)
-        if (prog[i] < prog[lo]) lo = i;
+        if (when(prog[i]) < when(prog[lo])) lo = i;
+      // which words of the exchange area of that layer never received their tag
+      if (ll_dev && last_plan_ll.ll_words > 0) {
+        const FusedPlan& fp = last_plan_ll;
+        const int layer = prog[lo] % 1000, step = prog[lo] / 10000, code = prog[lo] / 1000 % 10;
+        const int L = model->dims.n_layers;
+        const int src_layer = code == 1 ? layer - 1 : layer;       // phase A waits for the previous layer's reduce
+        if (src_layer >= 0 && src_layer < L) {
+          const unsigned want = fp.tag0 + (unsigned)step * (unsigned)(L + 1) + (unsigned)src_layer + 1u;
+          std::vector<fu_u64> words((size_t)fp.ll_words);
+          B2_CUDA(cudaMemcpy(words.data(), ll_dev + (size_t)(src_layer & 1) * fp.ll_words, sizeof(fu_u64) * fp.ll_words,
+                             cudaMemcpyDeviceToHost));
+          auto count = [&](int off, int n) {
+            int bad = 0, first = -1;
+            for (int i = 0; i < n; ++i)
+              if ((unsigned)(words[off + i] >> 32) != want) { if (first < 0) first = i; ++bad; }
+            return std::to_string(bad) + "/" + std::to_string(n) + (bad ? " (first " + std::to_string(first) + ")" : "");
+          };
+          const int d = model->dims.d;
+          detail += "; untagged words of layer " + std::to_string(src_layer) + ": qkv " + count(fp.ll_qkv, last_ncols * model->dims.nqkv()) +
+                    ", o " + count(fp.ll_o, dargs.o_slices * last_ncols * d) + ", ffn partials " +
+                    count(fp.ll_fpart, fp.nprod * last_ncols * d) + ", ffn out " + count(fp.ll_f, last_ncols * d);
+        }
+      }
       detail += "; least advanced CTA " + std::to_string(lo) + " at phase code " + std::to_string(prog[lo] / 1000 % 10) + ", layer " +
                 std::to_string(prog[lo] % 1000) + ", step " + std::to_string(prog[lo] / 10000);
     }
@@ -873,6 +906,8 @@ void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
     }
     pl.tag0 = ll_tag;
     ll_tag += need;
+    last_plan_ll = pl;
+    last_ncols = a.ncols;
     const void* kfn = decode_fused_kernel_for(d);
     raise_dyn_smem(kfn, smem);
     fu_u64* ll = ll_dev;

@@ -121,6 +121,8 @@ class Executor {
   fu_u64* ll_dev = nullptr;
   size_t ll_bytes = 0;
   unsigned ll_tag = 0;
+  FusedPlan last_plan_ll{};         // plan of the last chained launch (diagnostics of a wait that gave up)
+  int last_ncols = 1;
   bool chained_ok = false;          // the model fits the chained kernel (with n_sessions columns)
   long long* trace_dev = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
