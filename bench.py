@@ -32,8 +32,13 @@ import __graft_entry__ as graft  # noqa: E402
 
 PREFILL_TOKENS = 1024
 DECODE_STEPS = 256
-# DRAM bytes per decode step in the ncu capture under profiles/ (a launch of two steps read 1082.0 MB and wrote 32.0 MB)
-DECODE_DRAM_BYTES_PER_STEP = 557.0e6
+# DRAM bytes per decode step: an ncu capture (2026-11-25) of one launch of two decode steps of the chained
+# kernel read 1079.5 MB and wrote 48.3 MB
+DECODE_DRAM_BYTES_PER_STEP = 563.9e6
+# The CPU arm's sample of the workload, used by `--impl reference` and by the in-line `cpu_baseline` alike:
+# the full 1024-token prefill once, then short runs of greedy decode steps that stay inside the protocol's
+# context range (1024 .. 1280 positions).
+CPU_DECODE_TOKENS_PER_STEP = 8
 METRIC = "decode tok/s (256 greedy steps after a 1024-token prefill), Gemma3-1B-shaped int4, batch 1 per GPU"
 
 
@@ -120,26 +125,38 @@ class ClockSampler(threading.Thread):
         return {"sm_mhz": med, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": len(self.samples)}
 
 
-def cpu_sample(rec, cfg, prefill_tokens: int, decode_steps: int, repeats: int = 1):
-    """Times the CPU oracle on a bounded sample: prefill of `prefill_tokens` ids, then
-    `decode_steps` greedy steps at that context.  Returns (prefill tok/s, decode tok/s)."""
-    from oracle import oracle as orc
-    model = orc.OracleModel(rec)
-    ids = np.random.Generator(np.random.PCG64(cfg.seed)).integers(0, cfg.vocab, prefill_tokens + 1).astype(np.int32)
-    best_p, best_d = 0.0, 0.0
-    for _ in range(repeats):
-        ex = orc.OracleExecutor(model)
+class CpuArm:
+    """The CPU oracle on the benchmark workload: `prefill()` runs the whole 1024-id prompt (timed once),
+    `decode_step(n)` times n greedy steps that continue from there (context 1024 + steps so far)."""
+
+    def __init__(self, rec, cfg) -> None:
+        from oracle import oracle as orc
+        self.model = orc.OracleModel(rec)
+        self.ex = orc.OracleExecutor(self.model)
+        self.ids = np.random.Generator(np.random.PCG64(cfg.seed)).integers(0, cfg.vocab, PREFILL_TOKENS).astype(np.int32)
+        self.done = 0
+
+    def prefill(self) -> float:
         t0 = time.perf_counter()
-        assert ex.prefill(ids) == 0
-        t1 = time.perf_counter()
-        for _ in range(decode_steps):
-            rc, _tok = ex.decode_token()
+        assert self.ex.prefill(self.ids) == 0
+        self.done = 0
+        return PREFILL_TOKENS / (time.perf_counter() - t0)
+
+    def decode_step(self, n: int) -> float:
+        if self.done + n > DECODE_STEPS:          # stay inside the protocol's context range
+            self.ex.reset()
+            self.prefill()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            rc, _tok = self.ex.decode_token()
             assert rc == 0
-        t2 = time.perf_counter()
-        best_p = max(best_p, prefill_tokens / (t1 - t0))
-        best_d = max(best_d, decode_steps / (t2 - t1))
-        ex.close()
-    return best_p, best_d
+        self.done += n
+        return n / (time.perf_counter() - t0)
+
+
+def cpu_sample_text(n: int) -> str:
+    return (f"CPU oracle port (plain C, OpenMP, all host threads), same weights and seeded prompt: the {PREFILL_TOKENS}-id "
+            f"prefill once, then {n} greedy decode steps per bench step at context {PREFILL_TOKENS}+")
 
 
 def host_threads() -> int:
@@ -163,34 +180,40 @@ def use_all_host_threads() -> None:
         os.environ["OMP_NUM_THREADS"] = os.environ.get("B200LM_CPU_THREADS", str(n))
 
 
+def workload_config(cfg, world: int, decode_mode: int) -> dict:
+    return {"workload": f"{cfg.name}: {PREFILL_TOKENS}-token prefill + {DECODE_STEPS} greedy decode steps, batch 1 per GPU",
+            "seed": cfg.seed, "kv_cache": "fp32" if cfg.kv_dtype == 0 else "bf16", "context": cfg.max_ctx,
+            "sessions": world, "parallelism": f"independent sessions x{world}, no collective",
+            "l2": "every decode step streams 537 MB of weights and KV (> 126 MB L2); no flush needed",
+            "decode_mode": "persistent kernel" if decode_mode in (0, 2, 4) else "one kernel per phase (CUDA graph)"}
+
+
 def run_reference(args, rank: int) -> None:
     if rank != 0:
         return
     use_all_host_threads()
     cfg, rec, _ = load_model(args.model)
-    pt, ds = 32, 8
-    sample = (f"CPU oracle port (plain C, OpenMP): prefill of {pt} seeded ids then {ds} greedy decode steps at that "
-              f"context, same weights; the full protocol is {PREFILL_TOKENS}+{DECODE_STEPS}")
-    vals_p, vals_d = [], []
+    n = max(1, min(CPU_DECODE_TOKENS_PER_STEP, DECODE_STEPS // max(1, args.warmup + args.steps)))
+    arm = CpuArm(rec, cfg)
     t_all = time.perf_counter()
+    prefill_tok_s = arm.prefill()
+    vals = []
     for i in range(args.warmup + args.steps):
-        p, d = cpu_sample(rec, cfg, pt, ds)
+        v = arm.decode_step(n)
         if i >= args.warmup:
-            vals_p.append(p)
-            vals_d.append(d)
+            vals.append(v)
     wall = time.perf_counter() - t_all
-    value = float(np.mean(vals_d))
+    value = float(np.mean(vals))
     cores = host_threads()
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": 1000.0 * (pt / float(np.mean(vals_p)) + ds / value), "higher_is_better": True,
+        "ms_per_step": 1000.0 * n / value, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights x fp32 activations (CPU)", "data": "synthetic",
-        "config": {"workload": f"{cfg.name}: {PREFILL_TOKENS}-token prefill + {DECODE_STEPS} decode steps, batch 1",
-                   "seed": cfg.seed, "sample": f"{pt}+{ds} tokens per step"},
-        "prefill": {"value": float(np.mean(vals_p)), "unit": "tok/s"},
-        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample,
-                         "prefill_tok_s": float(np.mean(vals_p))},
+        "config": workload_config(cfg, 1, 0),
+        "prefill": {"value": prefill_tok_s, "unit": "tok/s"},
+        "cpu_baseline": {"value": value, "unit": "tok/s", "cores": cores, "kind": "port", "sample": cpu_sample_text(n),
+                         "prefill_tok_s": prefill_tok_s},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0, "wall_s": wall,
         "note": "the reference's LiteRT/XNNPACK CPU backend cannot be built here; this is the CPU restatement",
@@ -380,11 +403,7 @@ def main() -> None:
         "warmup": args.warmup, "ms_per_step": (pf_total + dec_total) / args.steps, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "int4 weights; int8x3 activations (decode), bf16 MMA (prefill), fp32 accumulate",
         "data": "synthetic",
-        "config": {"workload": f"{cfg.name}: {PREFILL_TOKENS}-token prefill + {DECODE_STEPS} greedy decode steps, batch 1 per GPU",
-                   "seed": cfg.seed, "kv_cache": "fp32" if cfg.kv_dtype == 0 else "bf16", "context": cfg.max_ctx,
-                   "sessions": world, "parallelism": f"independent sessions x{world}, no collective",
-                   "l2": "every decode step streams 537 MB of weights and KV (> 126 MB L2); no flush needed",
-                   "decode_mode": "persistent kernel" if args.decode_mode in (0, 2) else "one kernel per phase (CUDA graph)"},
+        "config": workload_config(cfg, world, args.decode_mode),
         "prefill": {"value": prefill_tok_s, "unit": "tok/s", "ms": per_gpu_pf_ms,
                     "roofline": {"bound": "tensor", "achieved": achieved_tf, "peak": peaks["bf16_tflops"],
                                  "unit": "TFLOP/s", "frac": achieved_tf / peaks["bf16_tflops"], "traffic": None,
@@ -396,18 +415,20 @@ def main() -> None:
         "gpu_launches": int(launches),
         "roofline": {"bound": "hbm", "achieved": achieved_gbs, "peak": peaks["hbm_gbs"], "unit": "GB/s",
                      "frac": achieved_gbs / peaks["hbm_gbs"], "traffic": DECODE_DRAM_BYTES_PER_STEP, "of": peaks["source"],
-                     "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum of one decode-step launch, from the "
-                                     "ncu capture summarised in profiles/decode_stream_kernel_gemma3-1b.md",
+                     "traffic_note": "dram__bytes_read.sum + dram__bytes_write.sum per decode step, from an ncu capture of "
+                                     "one two-step launch of the decode kernel",
                      "kernel": "decode step (all phases)", "algorithmic_bytes_per_token": bytes_per_tok,
                      "frac_of_nominal_8TBs": achieved_gbs / 8000.0},
     }
     if not args.no_cpu_baseline and world == 1:
-        pt, ds = 256, 256        # about 10-15 s of CPU work on 16 cores
+        # the same sample as `--impl reference`: about 20 s of CPU work on 16 cores
         t0 = time.perf_counter()
-        p, d = cpu_sample(rec, cfg, pt, ds)
+        arm = CpuArm(rec, cfg)
+        p = arm.prefill()
+        d = float(np.mean([arm.decode_step(CPU_DECODE_TOKENS_PER_STEP) for _ in range(4)][1:]))
         line["cpu_baseline"] = {"value": d, "unit": "tok/s", "cores": host_threads(), "kind": "port",
                                 "prefill_tok_s": p, "wall_s": time.perf_counter() - t0,
-                                "sample": f"CPU oracle port: prefill of {pt} ids then {ds} greedy decode steps, same weights"}
+                                "sample": cpu_sample_text(CPU_DECODE_TOKENS_PER_STEP)}
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

@@ -13,18 +13,24 @@
 // must be 1 and the id tensor non-empty (llm_litert_compiled_model_executor.cc:92-97),
 // an explicit decode id must be exactly one int32 (:303-315).
 //
-// Built against the real headers when B200LM_WITH_LITERT_LM is defined (the
-// tensor-buffer accessors then go through runtime/util/convert_tensor_buffer.h),
-// otherwise against litert_shim.h.
+// ONE body for both builds: against the real headers when B200LM_WITH_LITERT_LM is
+// defined, otherwise against litert_shim.h, which offers the same names and
+// signatures for the subset used here (TensorType().Layout().Dimensions(),
+// ReferTensorBufferAsSpan, TensorBufferScopedLock::Create, CreateTensorBuffer).
 #pragma once
+#include <atomic>
+#include <chrono>
 #include <cstdlib>
 #include <memory>
 #include <string>
+#include <thread>
+#include <utility>
 
 #include "b200lm.h"
 
 #ifdef B200LM_WITH_LITERT_LM
 #include "runtime/executor/llm_executor_base.h"
+#include "runtime/executor/llm_executor_settings.h"
 #include "runtime/util/convert_tensor_buffer.h"
 #else
 #include "litert_shim.h"
@@ -34,22 +40,25 @@ namespace litert::lm {
 
 class B200LlmExecutor : public LlmExecutorBase {
  public:
-  // model_path: a `.litertlm` file holding an int4 decoder weights record.
-  static absl::StatusOr<std::unique_ptr<B200LlmExecutor>> Create(const std::string& model_path,
-                                                                 const B200LmConfig& config) {
+  // model_path: a `.litertlm` file holding an int4 decoder weights record.  `settings`
+  // is what the engine built for this executor (LlmExecutorSettings::CreateDefault);
+  // its max_num_tokens is overwritten with the capacity of the KV cache, which is
+  // what GetExecutorSettings() must report (runtime/core/pipeline.cc:51-62).
+  static absl::StatusOr<std::unique_ptr<B200LlmExecutor>> Create(const std::string& model_path, const B200LmConfig& config,
+                                                                 LlmExecutorSettings settings) {
     B200LmExecutor* h = nullptr;
     char* err = nullptr;
     int rc = B200Lm_Create(&config, nullptr, 0, model_path.c_str(), &h, &err);
     if (rc != 0) return ToStatus(rc, err);
-    return std::unique_ptr<B200LlmExecutor>(new B200LlmExecutor(h));
+    return std::unique_ptr<B200LlmExecutor>(new B200LlmExecutor(h, std::move(settings)));
   }
-  static absl::StatusOr<std::unique_ptr<B200LlmExecutor>> CreateFromBytes(const void* bytes, uint64_t n,
-                                                                          const B200LmConfig& config) {
+  static absl::StatusOr<std::unique_ptr<B200LlmExecutor>> CreateFromBytes(const void* bytes, uint64_t n, const B200LmConfig& config,
+                                                                          LlmExecutorSettings settings) {
     B200LmExecutor* h = nullptr;
     char* err = nullptr;
     int rc = B200Lm_Create(&config, bytes, n, nullptr, &h, &err);
     if (rc != 0) return ToStatus(rc, err);
-    return std::unique_ptr<B200LlmExecutor>(new B200LlmExecutor(h));
+    return std::unique_ptr<B200LlmExecutor>(new B200LlmExecutor(h, std::move(settings)));
   }
   ~B200LlmExecutor() override { B200Lm_Destroy(h_); }
 
@@ -59,53 +68,81 @@ class B200LlmExecutor : public LlmExecutorBase {
     auto ids_or = inputs.GetTextTokenIdsPtr();
     if (!ids_or.ok()) return ids_or.status();
     const ::litert::TensorBuffer& ids = **ids_or;
-    const int32_t* data = nullptr;
-    int batch = 0, len = 0;
-    absl::Status st = ViewIds(ids, &data, &batch, &len);
-    if (!st.ok()) return st;
-    if (batch != 1) return absl::InternalError("Only batch size 1 is accepted.");
-    if (len <= 0) return absl::InternalError("Prefill token ids must be non-empty.");
-    // std::atomic_bool is lock-free and one byte wide here; the C ABI polls an int32 flag,
-    // so the adapter mirrors the flag into one before the call.
+    auto type = ids.TensorType();
+    if (!type) return absl::InternalError("token ids have no tensor type");
+    auto dims = type->Layout().Dimensions();
+    if (dims.size() != 2) return absl::InvalidArgumentError("token ids must be [batch, sequence_length]");
+    auto span = ReferTensorBufferAsSpan<int32_t>(ids);
+    if (!span) return absl::InvalidArgumentError("token ids must be int32 in host memory");
+    if (dims[0] != 1) return absl::InternalError("Only batch size 1 is accepted.");
+    if (dims[1] <= 0 || span->empty()) return absl::InternalError("Prefill token ids must be non-empty.");
+    // The C ABI polls an int32 word between work groups; the caller's flag is a
+    // std::atomic_bool.  While the call runs, a helper thread mirrors the flag into
+    // the word, so a cancel raised in the middle of a long prompt is seen at the
+    // next work group, not only one raised before the call.
     volatile int32_t cancel_word = 0;
     const std::atomic_bool* cancel = params.GetCancelFlag();
-    if (cancel != nullptr && cancel->load()) cancel_word = 1;
+    std::atomic<bool> call_done{false};
+    std::thread mirror;
+    if (cancel != nullptr) {
+      if (cancel->load()) cancel_word = 1;
+      mirror = std::thread([&] {
+        while (!call_done.load(std::memory_order_acquire)) {
+          if (cancel->load()) cancel_word = 1;
+          std::this_thread::sleep_for(std::chrono::microseconds(100));
+        }
+      });
+    }
     char* err = nullptr;
-    int rc = B200Lm_Prefill(h_, data, len, params.GetWaitForCompletion() ? 1 : 0, cancel ? &cancel_word : nullptr, &err);
+    int rc = B200Lm_Prefill(h_, span->data(), (int32_t)dims[1], params.GetWaitForCompletion() ? 1 : 0,
+                            cancel ? &cancel_word : nullptr, &err);
+    if (mirror.joinable()) {
+      call_done.store(true, std::memory_order_release);
+      mirror.join();
+    }
     return ToStatus(rc, err);
   }
 
   absl::Status Decode(::litert::TensorBuffer& output_tokens) override {
-    if (output_tokens.Size() < sizeof(int32_t)) return absl::InvalidArgumentError("output_tokens must hold one int32");
+    auto size = output_tokens.Size();
+    if (!size || *size < sizeof(int32_t)) return absl::InvalidArgumentError("output_tokens must hold one int32");
     char* err = nullptr;
     int32_t id = -1;
     int rc = B200Lm_DecodeToken(h_, &id, &err);
     if (rc != 0) return ToStatus(rc, err);
-    static_cast<int32_t*>(LockForWrite(output_tokens))[0] = id;
+    // the lock lives until the id has been written
+    auto lock_and_addr = ::litert::TensorBufferScopedLock::Create(output_tokens, ::litert::TensorBuffer::LockMode::kWrite);
+    if (!lock_and_addr) return absl::InternalError("cannot map output_tokens");
+    static_cast<int32_t*>(lock_and_addr->second)[0] = id;
     return absl::OkStatus();
   }
 
   absl::Status Decode(const ExecutorInputs& inputs, ::litert::TensorBuffer& output_logits) override {
     int vocab = 0;
     B200Lm_GetVocabSize(h_, &vocab, nullptr);
-    if (output_logits.Size() < sizeof(float) * (size_t)vocab)
+    auto size = output_logits.Size();
+    if (!size || *size < sizeof(float) * (size_t)vocab)
       return absl::InvalidArgumentError("output_logits is smaller than [1, 1, vocab] float32");
     int32_t id = 0;
     bool has_id = false;
     absl::Status st = ExplicitId(inputs, &id, &has_id);
     if (!st.ok()) return st;
+    // the lock lives across the call that writes the logits
+    auto lock_and_addr = ::litert::TensorBufferScopedLock::Create(output_logits, ::litert::TensorBuffer::LockMode::kWrite);
+    if (!lock_and_addr) return absl::InternalError("cannot map output_logits");
     char* err = nullptr;
-    int rc = B200Lm_DecodeLogits(h_, has_id ? &id : nullptr, static_cast<float*>(LockForWrite(output_logits)), &err);
+    int rc = B200Lm_DecodeLogits(h_, has_id ? &id : nullptr, static_cast<float*>(lock_and_addr->second), &err);
     return ToStatus(rc, err);
   }
 
   absl::StatusOr<::litert::TensorBuffer> DecodeLogits(const ExecutorInputs& inputs) override {
     int vocab = 0;
     B200Lm_GetVocabSize(h_, &vocab, nullptr);
-    ::litert::TensorBuffer logits = NewHostBuffer(vocab);
-    absl::Status st = Decode(inputs, logits);
+    auto logits = CreateTensorBuffer<float>({1, 1, vocab});       // as fake_llm_executor.cc:159-161 shapes them
+    if (!logits) return absl::InternalError("cannot allocate the logits buffer");
+    absl::Status st = Decode(inputs, *logits);
     if (!st.ok()) return st;
-    return logits;
+    return std::move(*logits);
   }
 
   absl::string_view ExecutorBackendName() const override { return B200Lm_BackendName(); }
@@ -126,13 +163,9 @@ class B200LlmExecutor : public LlmExecutorBase {
     return v;
   }
 
-  // The value LlmExecutorSettings::GetMaxNumTokens() must report for this executor,
-  // otherwise the pipeline assumes 4096 (runtime/core/pipeline.cc:51-62).
-  int GetMaxNumTokens() const {
-    int v = 0;
-    B200Lm_GetMaxNumTokens(h_, &v, nullptr);
-    return v;
-  }
+  // Settings whose GetMaxNumTokens() is the KV capacity: without this override the
+  // caller loop assumes 4096 tokens (runtime/core/pipeline.cc:51-62).
+  absl::StatusOr<LlmExecutorSettings> GetExecutorSettings() const override { return settings_; }
 
   absl::Status Reset() override {
     char* err = nullptr;
@@ -140,7 +173,10 @@ class B200LlmExecutor : public LlmExecutorBase {
   }
 
  private:
-  explicit B200LlmExecutor(B200LmExecutor* h) : h_(h) {}
+  B200LlmExecutor(B200LmExecutor* h, LlmExecutorSettings settings) : h_(h), settings_(std::move(settings)) {
+    int v = 0;
+    if (B200Lm_GetMaxNumTokens(h_, &v, nullptr) == 0 && v > 0) settings_.SetMaxNumTokens((uint64_t)v);
+  }
 
   static absl::Status ToStatus(int rc, char* err) {
     if (rc == 0) return absl::OkStatus();
@@ -148,37 +184,6 @@ class B200LlmExecutor : public LlmExecutorBase {
     free(err);                                   // the library mallocs, the caller frees
     return absl::Status(static_cast<absl::StatusCode>(rc), msg);
   }
-
-#ifdef B200LM_WITH_LITERT_LM
-  static absl::Status ViewIds(const ::litert::TensorBuffer& ids, const int32_t** data, int* batch, int* len) {
-    auto type = ids.TensorType();
-    if (!type) return absl::InternalError("token ids have no tensor type");
-    auto dims = type->Layout().Dimensions();
-    if (dims.size() != 2) return absl::InvalidArgumentError("token ids must be [batch, sequence_length]");
-    auto span = ReferTensorBufferAsSpan<int32_t>(ids);
-    if (!span) return absl::InvalidArgumentError("token ids must be int32 in host memory");
-    *data = span->data(); *batch = dims[0]; *len = dims[1];
-    return absl::OkStatus();
-  }
-  static void* LockForWrite(::litert::TensorBuffer& b) {
-    auto lock = ::litert::TensorBufferScopedLock::Create(b, ::litert::TensorBuffer::LockMode::kWrite);
-    return lock ? lock->second : nullptr;
-  }
-  static ::litert::TensorBuffer NewHostBuffer(int vocab) { return std::move(*CreateTensorBuffer<float>({1, 1, vocab})); }
-#else
-  static absl::Status ViewIds(const ::litert::TensorBuffer& ids, const int32_t** data, int* batch, int* len) {
-    if (ids.GetElementType() != ::litert::ElementType::Int32 || !ids.IsHostMemory())
-      return absl::InvalidArgumentError("token ids must be int32 in host memory");
-    const auto& dims = ids.GetDimensions();
-    if (dims.size() != 2) return absl::InvalidArgumentError("token ids must be [batch, sequence_length]");
-    *data = static_cast<const int32_t*>(ids.Lock()); *batch = dims[0]; *len = dims[1];
-    return absl::OkStatus();
-  }
-  static void* LockForWrite(::litert::TensorBuffer& b) { return b.Lock(); }
-  static ::litert::TensorBuffer NewHostBuffer(int vocab) {
-    return ::litert::TensorBuffer::CreateManagedHost(::litert::ElementType::Float32, {1, 1, vocab});
-  }
-#endif
 
   // An explicit id wins over the pending one and must be exactly one int32
   // (llm_litert_compiled_model_executor.cc:303-315).
@@ -188,19 +193,18 @@ class B200LlmExecutor : public LlmExecutorBase {
     auto ids_or = inputs.GetTextTokenIdsPtr();
     if (!ids_or.ok()) return absl::OkStatus();
     const ::litert::TensorBuffer& ids = **ids_or;
-    size_t bytes = ids.PackedSize();
-    if (bytes == 0) return absl::OkStatus();
-    if (bytes != sizeof(int32_t)) return absl::InternalError("Decode accepts a single token id.");
-    const int32_t* data = nullptr;
-    int batch = 0, len = 0;
-    absl::Status st = ViewIds(ids, &data, &batch, &len);
-    if (!st.ok()) return st;
-    *id = data[0];
+    auto bytes = ids.PackedSize();
+    if (!bytes || *bytes == 0) return absl::OkStatus();
+    if (*bytes != sizeof(int32_t)) return absl::InternalError("Decode accepts a single token id.");
+    auto span = ReferTensorBufferAsSpan<int32_t>(ids);
+    if (!span) return absl::InvalidArgumentError("token ids must be int32 in host memory");
+    *id = (*span)[0];
     *has_id = true;
     return absl::OkStatus();
   }
 
   B200LmExecutor* h_;
+  LlmExecutorSettings settings_;
 };
 
 }  // namespace litert::lm

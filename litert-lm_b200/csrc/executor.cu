@@ -442,7 +442,7 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   e->decode_mode = cfg.decode_mode == B200LM_DECODE_AUTO ? B200LM_DECODE_CHAINED : cfg.decode_mode;
   const int esz = d.kv_dtype == 0 ? 4 : 2;
   // ---- paged KV cache
-  e->pages_per_seq = (d.max_ctx + kPage - 1) / kPage;
+  e->pages_per_seq = (e->max_num_tokens + kPage - 1) / kPage;     // the cache holds max_num_tokens positions per session
   e->n_sessions = cfg.n_sessions > 0 ? cfg.n_sessions : 1;
   B2_CHECK(e->n_sessions <= kMaxCols, kInvalidArgument,
            "n_sessions exceeds the " + std::to_string(kMaxCols) + " sessions one decode step can carry");

@@ -57,7 +57,23 @@ def test_adapter_matches_c_abi(driver, pkg, models, tmp_path):
     assert [int(t) for t in out["tokens"].strip(",").split(",")] == want
     logits = ex.DecodeLogits(int(ids[0])).ravel()
     assert out["logits_dims"] == "3" and int(out["logits_argmax"]) == int(np.argmax(logits))
+    assert out["live_locks"] == "0"                                # no mapping outlives the call that wrote the logits
+    assert out["max_num_tokens"] == str(cfg.max_ctx)               # GetExecutorSettings().GetMaxNumTokens() = KV capacity
+    assert out["cancelled_prefill_code"] == "1" and out["float_ids_code"] == "3"
     assert out["step_end"] == str(ex.GetCurrentStep())
     assert out["undersized_logits_code"] == "3"
     assert out["reset_code"] == "0" and out["step_after_reset"] == "0"
     assert out["decode_without_id_code"] == "3"
+
+
+@pytest.mark.gpu
+def test_executor_settings_report_the_kv_capacity_of_a_long_context_model(driver, mio, tmp_path):
+    """The caller loop falls back to 4096 tokens when GetExecutorSettings is not implemented
+    (runtime/core/pipeline.cc:51-62); an 8192-position model must report 8192."""
+    import dataclasses
+    cfg = dataclasses.replace(mio.config_tiny(), max_ctx=8192)
+    img = mio.export_model_litertlm(cfg, mio.build_weights_record(cfg))
+    path = tmp_path / "tiny8k.litertlm"
+    path.write_bytes(img)
+    out = run_driver(driver, str(path), 2, seeded_ids(0, cfg.vocab, 12))
+    assert out["prefill_code"] == "0" and out["max_num_tokens"] == "8192"
