@@ -221,6 +221,95 @@ def run_reference(args, rank: int) -> None:
     print(json.dumps(line), flush=True)
 
 
+def run_cfg4(args, pkg, cfg, img, stream, rank: int, world: int, local_rank: int) -> None:
+    """BASELINE config 4: `--sessions` concurrent sessions (1024-id prompt + 256 greedy steps each) of the
+    4B-shaped model, sharded over the ranks with no collective on the data path.  On a GPU the sessions run
+    in lockstep groups (one pass over the weights per decode step for a whole group) over ONE weight copy;
+    the group size is the largest the decode kernels hold for this model."""
+    import torch
+    import torch.distributed as dist
+    mine = pkg.sharding.shard_sessions(args.sessions, world, rank)
+    cap = PREFILL_TOKENS + DECODE_STEPS + 256
+    owner, group = None, 4
+    while owner is None:
+        try:
+            owner = pkg.B200LlmExecutor(img, device=local_rank, stream=stream.cuda_stream, n_sessions=group, max_num_tokens=cap)
+        except pkg.StatusError:
+            if group == 1:
+                raise
+            group //= 2
+    groups = [mine[i:i + group] for i in range(0, len(mine), group)]
+    execs = [owner]
+    for g in groups[1:]:
+        execs.append(owner.CreateShared(n_sessions=group, max_num_tokens=cap, stream=stream.cuda_stream))
+    prompts = {sid: np.random.Generator(np.random.PCG64(pkg.sharding.session_seed(cfg.seed, sid))).integers(
+        0, cfg.vocab, PREFILL_TOKENS).astype(np.int32) for sid in mine}
+
+    def step():
+        pf, dec = 0.0, 0.0
+        for ex, g in zip(execs, groups):
+            e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+            for i in range(group):
+                ex.SelectSession(i)
+                ex.Reset()
+            e0.record(stream)
+            for i in range(group):        # a short last group repeats its last session: the lockstep step is the same work
+                ex.PrefillSession(i, prompts[g[min(i, len(g) - 1)]], wait_for_completion=False)
+            e1.record(stream)
+            if group > 1:
+                ex.DecodeTokensBatch(DECODE_STEPS)
+            else:
+                ex.DecodeTokens(DECODE_STEPS)
+            e2.record(stream)
+            e2.synchronize()
+            pf += e0.elapsed_time(e1)
+            dec += e1.elapsed_time(e2)
+        return pf, dec
+
+    def barrier():
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(1, min(args.warmup, 1))):
+        step()
+    sampler = ClockSampler(local_rank)
+    sampler.start()
+    barrier()
+    res = [step() for _ in range(max(1, min(args.steps, 3)))]
+    barrier()
+    clocks = sampler.finish()
+    n = len(res)
+    tok, (pf_ms, dec_ms) = pkg.sharding.reduce_throughput(n * len(mine) * DECODE_STEPS, [sum(r[0] for r in res), sum(r[1] for r in res)])
+    if rank != 0:
+        return
+    peaks = measured_peaks()
+    # per decode step of a group: the weights once, the KV of every session of the group
+    full = cfg.decode_bytes_per_token(s_lo=PREFILL_TOKENS, s_hi=PREFILL_TOKENS + DECODE_STEPS)
+    kv_only = full - cfg.decode_bytes_per_token(s_lo=0, s_hi=1)
+    per_step = full + (group - 1) * (kv_only + 4 * cfg.vocab)
+    steps_per_gpu = n * len(groups) * DECODE_STEPS
+    achieved = per_step * steps_per_gpu / (dec_ms / 1e3) / 1e9
+    line = {
+        "metric": "aggregate decode tok/s, 64 concurrent sessions (1024-token prompt + 256 greedy steps each), Gemma3-4B-shaped int4",
+        "value": tok / (dec_ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": n, "warmup": 1,
+        "ms_per_step": (pf_ms + dec_ms) / n, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 weights; int8 activation terms (decode), bf16 MMA (prefill), fp32 accumulate", "data": "synthetic",
+        "config": {"workload": f"{cfg.name}: {args.sessions} sessions x ({PREFILL_TOKENS}-token prefill + {DECODE_STEPS} decode steps), "
+                               f"sharded over {world} GPU(s), no collective", "seed": cfg.seed, "sessions_per_gpu": len(mine),
+                   "lockstep_group": group, "kv_cache": "fp32" if cfg.kv_dtype == 0 else "bf16", "context": cfg.max_ctx,
+                   "kv_capacity_per_session": cap},
+        "prefill": {"value": world * n * len(mine) * PREFILL_TOKENS / (pf_ms / 1e3), "unit": "tok/s"},
+        "decode_ms_per_group_step": dec_ms / steps_per_gpu,
+        "clocks": clocks,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
+                     "traffic": None, "of": peaks["source"], "algorithmic_bytes_per_group_step": per_step,
+                     "note": "weights once + KV of every session of the lockstep group, per GPU"},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     global DECODE_STEPS
     ap = argparse.ArgumentParser()
@@ -235,6 +324,9 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--batched-sessions", type=int, default=4,
                     help="extra leg: this many sessions per GPU decoded in lockstep (0 = skip)")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4"],
+                    help="cfg2: the headline protocol (default); cfg4: 64 concurrent sessions of the 4B shape, sharded over the GPUs")
+    ap.add_argument("--sessions", type=int, default=64, help="cfg4: concurrent sessions over all GPUs")
     ap.add_argument("--decode-steps", type=int, default=DECODE_STEPS,
                     help="decode steps per bench step (256 is the protocol; fewer only for profiler captures)")
     args = ap.parse_args()
@@ -245,6 +337,8 @@ def main() -> None:
     if args.impl == "reference":
         run_reference(args, rank)
         return
+    if args.workload == "cfg4" and args.model == "gemma3-1b":
+        args.model = "gemma3-4b"
 
     import torch
     import torch.distributed as dist
@@ -266,6 +360,11 @@ def main() -> None:
         cfg, rec, img = load_model(args.model)
     stream = torch.cuda.Stream()          # a real (non-default) stream: CUDA events below are recorded on it
     torch.cuda.set_stream(stream)
+    if args.workload == "cfg4":
+        run_cfg4(args, pkg, cfg, img, stream, rank, world, local_rank)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     ex = pkg.B200LlmExecutor(img, device=local_rank, decode_mode=args.decode_mode, prefill_gemm=args.prefill_gemm,
                              stream=stream.cuda_stream)
     # one session per GPU; session ids are sharded over the ranks, each with its own seeded prompt

@@ -59,6 +59,16 @@ typedef struct B200LmConfig {
   int32_t n_sessions;      /* sessions held by this executor, 1..4 (0 = 1); see
                               B200Lm_DecodeTokensBatch */
   int32_t reserved1;
+  /* Tensor parallelism (BASELINE config 5).  tp_world > 1: this executor is rank tp_rank of tp_world and
+   * the model image holds THAT RANK'S SHARD (query / kv heads and FFN columns split over the ranks, see
+   * model_io.shard_for_tensor_parallel); the partial O and down projections of the ranks are summed with an
+   * NCCL all-reduce on the executor's stream.  tp_unique_id points at the 128 bytes of an ncclUniqueId that
+   * rank 0 obtained from B200Lm_TpUniqueId and handed to every rank.  One process per GPU; every rank makes
+   * the same calls in the same order.  The reference has no multi-GPU path
+   * (runtime/executor/llm_litert_compiled_model_executor.cc:95 checks batch 1). */
+  int32_t tp_rank;
+  int32_t tp_world;
+  const void* tp_unique_id;
 } B200LmConfig;
 
 /* Replaces LlmLiteRtCompiledModelExecutor::Create
@@ -133,6 +143,10 @@ int B200Lm_Reset(B200LmExecutor* e, char** err);
 int B200Lm_GetVocabSize(B200LmExecutor* e, int32_t* out, char** err);
 int B200Lm_GetCurrentStep(B200LmExecutor* e, int32_t* out, char** err);
 int B200Lm_GetMaxNumTokens(B200LmExecutor* e, int32_t* out, char** err);
+
+/* 128 bytes of a fresh ncclUniqueId for a tensor-parallel group (call on one rank, give the bytes to all).
+ * No counterpart in the reference. */
+int B200Lm_TpUniqueId(void* out_128_bytes, char** err);
 
 /* The decode path this executor settled on (B200LM_DECODE_*): what AUTO resolved to, or
  * the fallback taken when the requested kernel does not fit the model.  No counterpart

@@ -47,14 +47,15 @@ class StatusError(RuntimeError):
 class B200LmConfig(C.Structure):
     _fields_ = [("struct_size", C.c_int32), ("device", C.c_int32), ("max_num_tokens", C.c_int32),
                 ("decode_mode", C.c_int32), ("prefill_gemm", C.c_int32), ("page_order", C.c_int32),
-                ("stream", C.c_void_p), ("n_sessions", C.c_int32), ("reserved1", C.c_int32)]
+                ("stream", C.c_void_p), ("n_sessions", C.c_int32), ("reserved1", C.c_int32),
+                ("tp_rank", C.c_int32), ("tp_world", C.c_int32), ("tp_unique_id", C.c_void_p)]
 
 
 _lib: Optional[C.CDLL] = None
 
 _EXEC_SYMBOLS = ["B200Lm_Create", "B200Lm_CreateShared", "B200Lm_Destroy", "B200Lm_Prefill", "B200Lm_DecodeLogits",
                  "B200Lm_DecodeToken", "B200Lm_DecodeTokens", "B200Lm_Reset", "B200Lm_GetVocabSize",
-                 "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_GetDecodeMode", "B200Lm_BackendName", "B200Lm_Synchronize",
+                 "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_GetDecodeMode", "B200Lm_TpUniqueId", "B200Lm_BackendName", "B200Lm_Synchronize",
                  "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount", "B200Lm_TraceDecodeStep",
                  "B200Lm_SelectSession", "B200Lm_GetNumSessions", "B200Lm_PrefillSession", "B200Lm_DecodeTokensBatch"]
 _OPS_SYMBOLS = ["B200LmOps_RepackW4T", "B200LmOps_RepackW4G", "B200LmOps_UnpackW4", "B200LmOps_GemvW4",
@@ -85,6 +86,7 @@ def load_library() -> C.CDLL:
         "B200Lm_GetCurrentStep": [vp, vp, errp],
         "B200Lm_GetMaxNumTokens": [vp, vp, errp],
         "B200Lm_GetDecodeMode": [vp, vp, errp],
+        "B200Lm_TpUniqueId": [vp, errp],
         "B200Lm_Synchronize": [vp, errp],
         "B200Lm_GetLastPrefillPlan": [vp, vp, vp, i32, vp, errp],
         "B200Lm_ReadKvRow": [vp, i32, i32, i32, i32, vp, vp, vp, errp],
@@ -115,6 +117,14 @@ def load_library() -> C.CDLL:
     lib.B200Lm_BackendName.restype = C.c_char_p
     _lib = lib
     return lib
+
+
+def tp_unique_id() -> bytes:
+    """128 bytes identifying a new tensor-parallel group (an ncclUniqueId): make it on one rank and hand
+    the same bytes to every rank's executor."""
+    buf = C.create_string_buffer(128)
+    _call("B200Lm_TpUniqueId", C.cast(buf, C.c_void_p))
+    return buf.raw
 
 
 _libc = C.CDLL(None)
@@ -151,10 +161,13 @@ class B200LlmExecutor:
 
     def __init__(self, model, device: int = 0, max_num_tokens: int = 0, decode_mode: int = DECODE_AUTO,
                  prefill_gemm: int = GEMM_AUTO, stream: int = 0, reversed_pages: bool = False,
-                 n_sessions: int = 1, _shared_from: "Optional[B200LlmExecutor]" = None) -> None:
+                 n_sessions: int = 1, tp_rank: int = 0, tp_world: int = 1, tp_unique_id: Optional[bytes] = None,
+                 _shared_from: "Optional[B200LlmExecutor]" = None) -> None:
         self._h = C.c_void_p()
+        self._tp_id = C.create_string_buffer(bytes(tp_unique_id), 128) if tp_unique_id is not None else None
         cfg = B200LmConfig(C.sizeof(B200LmConfig), device, max_num_tokens, decode_mode, prefill_gemm,
-                           1 if reversed_pages else 0, stream or None, n_sessions, 0)
+                           1 if reversed_pages else 0, stream or None, n_sessions, 0, tp_rank, tp_world,
+                           C.cast(self._tp_id, C.c_void_p) if self._tp_id is not None else None)
         if _shared_from is not None:
             _call("B200Lm_CreateShared", _shared_from._h, C.byref(cfg), C.byref(self._h))
         elif isinstance(model, (bytes, bytearray, memoryview)):

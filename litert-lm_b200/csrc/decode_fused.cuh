@@ -1628,7 +1628,11 @@ __device__ __forceinline__ unsigned fu_phase_head(const DecodeArgs& a, const Fus
     const int nq = ncols * nterms;
     const bool timed = a.trace_pts != nullptr;      // the timeline tool asks where the warps spend the phase
     long long t_wait = 0, t_mma = 0, t_fin = 0;
-    for (int i = warp; i < sh.h_n; i += kDecWarps) {
+    // A warp may wait for a slot only while the fill before it in that slot is already the warp's own
+    // past (an mbarrier wait tells apart two consecutive phases, not three): with fewer slots than warps
+    // only as many warps stream as there are slots.
+    const int nstream = min(kDecWarps, c.nslots);
+    for (int i = warp; i < sh.h_n && warp < nstream; i += nstream) {
       const unsigned fill = f0 + (unsigned)i;
       const long long t0 = timed ? clock64() : 0;
       fu_acquire(rg, c, fill);

@@ -395,6 +395,9 @@ Executor::~Executor() {
   cudaSetDevice(device);
   if (stream) cudaStreamSynchronize(stream);
   if (graph_exec) cudaGraphExecDestroy(graph_exec);
+  if (tp_comm) {
+    try { NcclApi::get().CommDestroy(tp_comm); } catch (...) {}
+  }
   for (void* p : allocations) cudaFree(p);
   for (int i = 0; i < kTokRing; ++i)
     if (tok_ring_done[i]) cudaEventDestroy(tok_ring_done[i]);
@@ -429,6 +432,16 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
     B2_CUDA(cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking));
     e->own_stream = true;
   }
+  if (cfg.tp_world > 1) {
+    B2_CHECK(cfg.tp_rank >= 0 && cfg.tp_rank < cfg.tp_world && cfg.tp_unique_id != nullptr, kInvalidArgument,
+             "tensor parallelism needs 0 <= tp_rank < tp_world and the group's unique id");
+    const NcclApi& nccl = NcclApi::get();
+    NcclApi::UniqueId id;
+    memcpy(&id, cfg.tp_unique_id, sizeof id);
+    nccl.check(nccl.CommInitRank(&e->tp_comm, cfg.tp_world, id, cfg.tp_rank), "ncclCommInitRank");
+    e->tp_rank = cfg.tp_rank;
+    e->tp_world = cfg.tp_world;
+  }
   e->max_num_tokens = cfg.max_num_tokens > 0 ? std::min(cfg.max_num_tokens, d.max_ctx) : d.max_ctx;
   B2_CHECK(cfg.prefill_gemm >= B200LM_GEMM_AUTO && cfg.prefill_gemm <= B200LM_GEMM_TCGEN05, kInvalidArgument,
            "prefill_gemm must be B200LM_GEMM_AUTO, _CHECK or _TCGEN05");
@@ -440,6 +453,8 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   B2_CHECK(cfg.decode_mode >= B200LM_DECODE_AUTO && cfg.decode_mode <= B200LM_DECODE_CHAINED, kInvalidArgument,
            "decode_mode must be one of B200LM_DECODE_*");
   e->decode_mode = cfg.decode_mode == B200LM_DECODE_AUTO ? B200LM_DECODE_CHAINED : cfg.decode_mode;
+  // a collective cannot run inside a persistent kernel: tensor-parallel decode is one kernel per phase
+  if (cfg.tp_world > 1) e->decode_mode = B200LM_DECODE_PHASE_KERNELS;
   const int esz = d.kv_dtype == 0 ? 4 : 2;
   // ---- paged KV cache
   e->pages_per_seq = (e->max_num_tokens + kPage - 1) / kPage;     // the cache holds max_num_tokens positions per session
@@ -638,6 +653,11 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   return e;
 }
 
+void Executor::tp_allreduce(float* buf, size_t count) {
+  const NcclApi& nccl = NcclApi::get();
+  nccl.check(nccl.AllReduce(buf, buf, count, kNcclFloat32, kNcclSum, tp_comm, stream), "ncclAllReduce");
+}
+
 void Executor::check_device_error(const char* where) {
   int err = 0;
   // err, barrier, steps_done and gave_up[4] are adjacent
@@ -821,6 +841,7 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
     int ks_o = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(T, (d.d + kTsRows - 1) / kTsRows, d.nq() / 64, n_sms) : 1;
     launch_gemm(stream, mode, tm_attn, pf_attn, L.wo, L.so, Gm.wo, Gm.so, T, d.d, d.nq(), ks_o, false, pf_parts,
                 nullptr, err, &launches);
+    if (tp_world > 1) tp_allreduce(pf_parts, (size_t)ks_o * T * d.d);
     launch_resid_norm(stream, pf_parts, ks_o, T, d, L.g_post_attn, L.g_pre_ffn, pf_xres, pf_h);
     ++launches;
     launch_gemm(stream, mode, tm_h, pf_h, L.wgu, L.sgu, Gm.wgu, Gm.sgu, T, 2 * d.ffn, d.d, 1, true, nullptr, pf_act,
@@ -828,6 +849,7 @@ void Executor::run_prefill_chunk(const int* tokens, int T, int start) {
     int ks_d = mode == B200LM_GEMM_TCGEN05 ? pick_ksplit(T, (d.d + kTsRows - 1) / kTsRows, d.ffn / 64, n_sms) : 1;
     launch_gemm(stream, mode, tm_act, pf_act, L.wdown, L.sdown, Gm.wdown, Gm.sdown, T, d.d, d.ffn, ks_d, false,
                 pf_parts, nullptr, err, &launches);
+    if (tp_world > 1) tp_allreduce(pf_parts, (size_t)ks_d * T * d.d);
     const float* g_next = li + 1 < d.n_layers ? model->layers_host[li + 1].g_pre_attn : nullptr;
     launch_resid_norm(stream, pf_parts, ks_d, T, d, L.g_post_ffn, g_next, pf_xres, pf_h);
     ++launches;
@@ -953,6 +975,22 @@ void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
   }
   B2_CHECK(ncols == 1, kFailedPrecondition, "batched decode needs a persistent decode mode");
   B2_CHECK(n_sessions == 1, kFailedPrecondition, "several sessions per executor need a persistent decode mode");
+  if (tp_world > 1) {
+    // the same phases, launched one by one, with the ranks' partial O and down outputs summed in between
+    for (int s = 0; s < nsteps; ++s) {
+      for (int li = 0; li < d.n_layers; ++li)
+        for (int ph = kPhQkv; ph <= kPhDown; ++ph) {
+          decode_phase_kernel<<<ncta, kDecThreads, dec_smem, stream>>>(dargs, ph, li);
+          if (ph == kPhOproj) tp_allreduce(dargs.opart, (size_t)dargs.o_slices * kMaxCols * d.d);
+          if (ph == kPhDown) tp_allreduce(dargs.fpart, (size_t)dargs.down_slices * kMaxCols * d.d);
+        }
+      decode_phase_kernel<<<ncta, kDecThreads, dec_smem, stream>>>(dargs, kPhHead, 0);
+      decode_phase_kernel<<<1, kDecThreads, dec_smem, stream>>>(dargs, kPhArgmax, ncta);
+    }
+    B2_CUDA(cudaGetLastError());
+    launches += (int64_t)nsteps * (5 * d.n_layers + 2);
+    return;
+  }
   if (!graph_exec) {
     cudaGraph_t graph;
     B2_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
@@ -1318,6 +1356,16 @@ int B200Lm_GetMaxNumTokens(B200LmExecutor* e, int32_t* out, char** err) {
   B2_API_BEGIN
   B2_CHECK(e && e->impl && out, kInvalidArgument, "null argument");
   *out = e->impl->max_num_tokens;
+  B2_API_END
+}
+
+int B200Lm_TpUniqueId(void* out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(out != nullptr, kInvalidArgument, "out is null");
+  const NcclApi& nccl = NcclApi::get();
+  NcclApi::UniqueId id;
+  nccl.check(nccl.GetUniqueId(&id), "ncclGetUniqueId");
+  memcpy(out, &id, sizeof id);
   B2_API_END
 }
 

@@ -11,6 +11,7 @@
 #include "common.cuh"
 #include "decode_ops.cuh"
 #include "decode_fused.cuh"
+#include "tp_nccl.h"
 
 namespace b200lm {
 
@@ -116,6 +117,10 @@ class Executor {
   size_t dec_smem = 0;
   size_t stream_smem = 0;
   int stream_half = 0;
+  // tensor parallelism: sum over the ranks of a buffer of partial projections, on the executor's stream
+  int tp_rank = 0, tp_world = 1;
+  NcclApi::Comm tp_comm = nullptr;
+  void tp_allreduce(float* buf, size_t count);
   unsigned barrier_epoch = 0;
   // chained decode kernel: exchange area (two parity copies of flag-carrying words) and the next free tag
   fu_u64* ll_dev = nullptr;

@@ -290,6 +290,40 @@ def build_weights_record(cfg: ModelConfig) -> bytes:
     return pack_weights_record(cfg, generate_tensors(cfg))
 
 
+def shard_for_tensor_parallel(cfg: ModelConfig, tensors: "Dict[str, np.ndarray]", rank: int, world: int):
+    """The sub-model one tensor-parallel rank holds: query / kv heads and FFN columns are split over the
+    ranks (W_q / W_k / W_v and gate / up by output rows, W_o and W_down by input columns), norms and the
+    tied embedding are replicated.  Quantised values and their per-row scales are SLICED, never
+    re-quantised, so the partial O and down outputs of the ranks add up exactly to the unsplit products;
+    the executor sums them across the ranks (all-reduce) before the post-norms.  Returns (config, tensors)
+    of a valid smaller model."""
+    hq, hkv, hd, f, d = cfg.n_q_heads, cfg.n_kv_heads, cfg.head_dim, cfg.ffn, cfg.d_model
+    if hq % world or hkv % world or f % world or (f // world) % 64 or ((hq // world) * hd) % 64:
+        raise ValueError("heads / ffn columns do not divide over the ranks in 64-wide units")
+    import dataclasses
+    hq_r, hkv_r, f_r = hq // world, hkv // world, f // world
+    sub = dataclasses.replace(cfg, name=f"{cfg.name}-tp{rank}of{world}", n_q_heads=hq_r, n_kv_heads=hkv_r, ffn=f_r)
+    out: Dict[str, np.ndarray] = {}
+    for nm, a in tensors.items():
+        base = nm.split(".")[-2] if nm.endswith((".q", ".scale")) else nm.split(".")[-1]
+        is_q, is_s = nm.endswith(".q"), nm.endswith(".scale")
+        if base == "wqkv":
+            rows = np.concatenate([np.arange(rank * hq_r * hd, (rank + 1) * hq_r * hd),
+                                   hq * hd + np.arange(rank * hkv_r * hd, (rank + 1) * hkv_r * hd),
+                                   (hq + hkv) * hd + np.arange(rank * hkv_r * hd, (rank + 1) * hkv_r * hd)])
+            out[nm] = np.ascontiguousarray(a[rows])
+        elif base in ("wgate", "wup"):
+            out[nm] = np.ascontiguousarray(a[rank * f_r:(rank + 1) * f_r])
+        elif base == "wo" and is_q:          # input columns = this rank's heads; two int4 per byte
+            out[nm] = np.ascontiguousarray(a[:, rank * hq_r * hd // 2:(rank + 1) * hq_r * hd // 2])
+        elif base == "wdown" and is_q:
+            out[nm] = np.ascontiguousarray(a[:, rank * f_r // 2:(rank + 1) * f_r // 2])
+        else:                                 # scales of W_o / W_down (per output row), norms, embedding
+            out[nm] = a
+        del is_s
+    return sub, out
+
+
 # --------------------------------------------------------------------------- flatbuffer (by hand)
 
 class _FbWriter:
