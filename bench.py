@@ -310,6 +310,75 @@ def run_cfg4(args, pkg, cfg, img, stream, rank: int, world: int, local_rank: int
     print(json.dumps(line), flush=True)
 
 
+def run_cfg5(args, pkg, rank: int, world: int, local_rank: int) -> None:
+    """BASELINE config 5's partitioning on `world` GPUs: query / kv heads and FFN columns split over the ranks,
+    an NCCL all-reduce after the O and the down projection.  The model is a slice of a few layers of the
+    27B shape (the full 62 layers take too long to generate on the host); one sequence, a 2048-id prompt,
+    256 greedy steps.  Reports tok/s and the share of the all-reduces in a decode step."""
+    import torch
+    import torch.distributed as dist
+    mio = pkg.model_io
+    cfg = mio.CONFIGS[args.model]()
+    tensors = mio.generate_tensors(cfg)
+    prompt_len = min(2048, cfg.max_ctx - DECODE_STEPS - 1)
+    ids = np.random.Generator(np.random.PCG64(cfg.seed)).integers(0, cfg.vocab, prompt_len).astype(np.int32)
+    stream = torch.cuda.Stream()
+    torch.cuda.set_stream(stream)
+    if world > 1:
+        sub_cfg, sub = mio.shard_for_tensor_parallel(cfg, tensors, rank, world)
+        ident = [pkg.tp_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(ident, src=0)
+        kw = dict(tp_rank=rank, tp_world=world, tp_unique_id=ident[0])
+    else:
+        sub_cfg, sub, kw = cfg, tensors, dict(decode_mode=pkg.DECODE_PHASE_KERNELS)
+    img = mio.export_model_litertlm(sub_cfg, mio.pack_weights_record(sub_cfg, sub))
+    del tensors, sub
+    ex = pkg.B200LlmExecutor(img, device=local_rank, stream=stream.cuda_stream, **kw)
+
+    def step():
+        ex.Reset()
+        e0, e1, e2 = (torch.cuda.Event(enable_timing=True) for _ in range(3))
+        e0.record(stream)
+        ex.Prefill(ids, wait_for_completion=False)
+        e1.record(stream)
+        toks = ex.DecodeTokens(DECODE_STEPS)
+        e2.record(stream)
+        e2.synchronize()
+        return e0.elapsed_time(e1), e1.elapsed_time(e2), toks
+
+    step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    res = [step() for _ in range(max(1, min(args.steps, 3)))]
+    pf = float(np.mean([r[0] for r in res]))
+    dec = float(np.mean([r[1] for r in res]))
+    t = torch.tensor([pf, dec], dtype=torch.float64, device="cuda")
+    ar_ms = 0.0
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        # the two buffers summed per layer: the O partials (one d-vector per head slice of the rank) and the down partials
+        ar_counts = [(cfg.n_q_heads // world) * cfg.d_model, 4 * cfg.d_model]
+        ar_ms = float(np.mean([ex.TpAllReduceProbe(c, 100) for c in ar_counts]))
+    if rank != 0:
+        return
+    pf, dec = float(t[0]), float(t[1])
+    n_ar = 2 * cfg.n_layers
+    line = {
+        "metric": "decode tok/s, one sequence, tensor parallel over the GPUs, Gemma3-27B layer geometry (slice)",
+        "value": DECODE_STEPS / (dec / 1e3), "unit": "tok/s", "n_gpus": world, "steps": len(res), "warmup": 1,
+        "ms_per_step": pf + dec, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int4 weights; int8 activation terms (decode), bf16 MMA (prefill), fp32 all-reduce", "data": "synthetic",
+        "config": {"workload": f"{cfg.name} ({cfg.n_layers} layers): {prompt_len}-token prefill + {DECODE_STEPS} decode steps, batch 1, "
+                               f"tensor parallel x{world}", "seed": cfg.seed, "decode": "one kernel per phase, all-reduce after O and down"},
+        "prefill": {"value": prompt_len / (pf / 1e3), "unit": "tok/s", "ms": pf},
+        "decode_ms_per_token": dec / DECODE_STEPS,
+        "allreduce": {"per_decode_step": n_ar, "ms_each": ar_ms, "share_of_decode_step": (n_ar * ar_ms) / (dec / DECODE_STEPS) if world > 1 else 0.0,
+                      "floats_each": [(cfg.n_q_heads // world) * cfg.d_model, 4 * cfg.d_model] if world > 1 else []},
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main() -> None:
     global DECODE_STEPS
     ap = argparse.ArgumentParser()
@@ -324,8 +393,9 @@ def main() -> None:
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--batched-sessions", type=int, default=4,
                     help="extra leg: this many sessions per GPU decoded in lockstep (0 = skip)")
-    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4"],
-                    help="cfg2: the headline protocol (default); cfg4: 64 concurrent sessions of the 4B shape, sharded over the GPUs")
+    ap.add_argument("--workload", default="cfg2", choices=["cfg2", "cfg4", "cfg5"],
+                    help="cfg2: the headline protocol (default); cfg4: 64 concurrent sessions of the 4B shape, sharded over the GPUs; "
+                         "cfg5: tensor parallelism over the GPUs at the 27B shape's layer geometry")
     ap.add_argument("--sessions", type=int, default=64, help="cfg4: concurrent sessions over all GPUs")
     ap.add_argument("--decode-steps", type=int, default=DECODE_STEPS,
                     help="decode steps per bench step (256 is the protocol; fewer only for profiler captures)")
@@ -339,6 +409,8 @@ def main() -> None:
         return
     if args.workload == "cfg4" and args.model == "gemma3-1b":
         args.model = "gemma3-4b"
+    if args.workload == "cfg5" and args.model == "gemma3-1b":
+        args.model = "gemma3-27b-slice"
 
     import torch
     import torch.distributed as dist
@@ -349,6 +421,11 @@ def main() -> None:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     graft.build()
     pkg = graft.load_package()
+    if args.workload == "cfg5":
+        run_cfg5(args, pkg, rank, world, local_rank)
+        if world > 1:
+            dist.destroy_process_group()
+        return
     if world > 1:
         # rank 0 generates (or finds) the cached model file; the others read it afterwards
         if rank == 0:

@@ -148,6 +148,11 @@ int B200Lm_GetMaxNumTokens(B200LmExecutor* e, int32_t* out, char** err);
  * No counterpart in the reference. */
 int B200Lm_TpUniqueId(void* out_128_bytes, char** err);
 
+/* Mean device time (ms) of one all-reduce of `count` floats over the executor's tensor-parallel group,
+ * measured with CUDA events over `iters` back-to-back calls: tells the share of the collectives in a
+ * decode step (two per layer).  Every rank must call it.  No counterpart in the reference. */
+int B200Lm_TpAllReduceProbe(B200LmExecutor* e, int64_t count, int32_t iters, float* ms_out, char** err);
+
 /* The decode path this executor settled on (B200LM_DECODE_*): what AUTO resolved to, or
  * the fallback taken when the requested kernel does not fit the model.  No counterpart
  * in the reference. */

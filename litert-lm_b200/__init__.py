@@ -55,7 +55,7 @@ _lib: Optional[C.CDLL] = None
 
 _EXEC_SYMBOLS = ["B200Lm_Create", "B200Lm_CreateShared", "B200Lm_Destroy", "B200Lm_Prefill", "B200Lm_DecodeLogits",
                  "B200Lm_DecodeToken", "B200Lm_DecodeTokens", "B200Lm_Reset", "B200Lm_GetVocabSize",
-                 "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_GetDecodeMode", "B200Lm_TpUniqueId", "B200Lm_BackendName", "B200Lm_Synchronize",
+                 "B200Lm_GetCurrentStep", "B200Lm_GetMaxNumTokens", "B200Lm_GetDecodeMode", "B200Lm_TpUniqueId", "B200Lm_TpAllReduceProbe", "B200Lm_BackendName", "B200Lm_Synchronize",
                  "B200Lm_GetLastPrefillPlan", "B200Lm_ReadKvRow", "B200Lm_GetLaunchCount", "B200Lm_TraceDecodeStep",
                  "B200Lm_SelectSession", "B200Lm_GetNumSessions", "B200Lm_PrefillSession", "B200Lm_DecodeTokensBatch"]
 _OPS_SYMBOLS = ["B200LmOps_RepackW4T", "B200LmOps_RepackW4G", "B200LmOps_UnpackW4", "B200LmOps_GemvW4",
@@ -87,6 +87,7 @@ def load_library() -> C.CDLL:
         "B200Lm_GetMaxNumTokens": [vp, vp, errp],
         "B200Lm_GetDecodeMode": [vp, vp, errp],
         "B200Lm_TpUniqueId": [vp, errp],
+        "B200Lm_TpAllReduceProbe": [vp, i64, i32, vp, errp],
         "B200Lm_Synchronize": [vp, errp],
         "B200Lm_GetLastPrefillPlan": [vp, vp, vp, i32, vp, errp],
         "B200Lm_ReadKvRow": [vp, i32, i32, i32, i32, vp, vp, vp, errp],
@@ -243,6 +244,12 @@ class B200LlmExecutor:
         v = C.c_int32(0)
         _call("B200Lm_GetDecodeMode", self._h, C.byref(v))
         return v.value
+
+    def TpAllReduceProbe(self, count: int, iters: int = 50) -> float:
+        """Mean device time in ms of one all-reduce of `count` floats over the tensor-parallel group."""
+        ms = C.c_float(0)
+        _call("B200Lm_TpAllReduceProbe", self._h, count, iters, C.byref(ms))
+        return ms.value
 
     def GetMaxNumTokens(self) -> int:
         v = C.c_int32()

@@ -981,8 +981,8 @@ void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
       for (int li = 0; li < d.n_layers; ++li)
         for (int ph = kPhQkv; ph <= kPhDown; ++ph) {
           decode_phase_kernel<<<ncta, kDecThreads, dec_smem, stream>>>(dargs, ph, li);
-          if (ph == kPhOproj) tp_allreduce(dargs.opart, (size_t)dargs.o_slices * kMaxCols * d.d);
-          if (ph == kPhDown) tp_allreduce(dargs.fpart, (size_t)dargs.down_slices * kMaxCols * d.d);
+          if (ph == kPhOproj) tp_allreduce(dargs.opart, (size_t)dargs.o_slices * dargs.ncols * d.d);
+          if (ph == kPhDown) tp_allreduce(dargs.fpart, (size_t)dargs.down_slices * dargs.ncols * d.d);
         }
       decode_phase_kernel<<<ncta, kDecThreads, dec_smem, stream>>>(dargs, kPhHead, 0);
       decode_phase_kernel<<<1, kDecThreads, dec_smem, stream>>>(dargs, kPhArgmax, ncta);
@@ -1366,6 +1366,32 @@ int B200Lm_TpUniqueId(void* out, char** err) {
   NcclApi::UniqueId id;
   nccl.check(nccl.GetUniqueId(&id), "ncclGetUniqueId");
   memcpy(out, &id, sizeof id);
+  B2_API_END
+}
+
+int B200Lm_TpAllReduceProbe(B200LmExecutor* e, int64_t count, int32_t iters, float* ms_out, char** err) {
+  B2_API_BEGIN
+  B2_CHECK(e && e->impl && ms_out && count > 0 && iters > 0, kInvalidArgument, "bad argument");
+  Executor& x = *e->impl;
+  B2_CHECK(x.tp_world > 1, kFailedPrecondition, "this executor is not tensor-parallel");
+  B2_CUDA(cudaSetDevice(x.device));
+  float* buf = nullptr;
+  B2_CUDA(cudaMalloc(&buf, sizeof(float) * (size_t)count));
+  B2_CUDA(cudaMemsetAsync(buf, 0, sizeof(float) * (size_t)count, x.stream));
+  cudaEvent_t e0, e1;
+  B2_CUDA(cudaEventCreate(&e0));
+  B2_CUDA(cudaEventCreate(&e1));
+  for (int i = 0; i < 3; ++i) x.tp_allreduce(buf, (size_t)count);
+  B2_CUDA(cudaEventRecord(e0, x.stream));
+  for (int i = 0; i < iters; ++i) x.tp_allreduce(buf, (size_t)count);
+  B2_CUDA(cudaEventRecord(e1, x.stream));
+  B2_CUDA(cudaEventSynchronize(e1));
+  float ms = 0.f;
+  B2_CUDA(cudaEventElapsedTime(&ms, e0, e1));
+  *ms_out = ms / (float)iters;
+  cudaEventDestroy(e0);
+  cudaEventDestroy(e1);
+  cudaFree(buf);
   B2_API_END
 }
 

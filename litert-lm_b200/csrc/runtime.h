@@ -74,10 +74,12 @@ class Executor {
   void check_device_error(const char* where);
   void trace_decode_step(int* out_id, long long* stamps, long long capacity, int* n_barriers, int* n_cta, int* khz);
   void read_kv_row(int layer, int is_v, int kv_head, int pos, float* out, int* page, int* slot);
+  void tp_allreduce(float* buf, size_t count);      // sum over the tensor-parallel ranks, in place, on `stream`
 
   std::shared_ptr<Model> model;
   int device = 0;
   int n_sms = 0;
+  int tp_rank = 0, tp_world = 1;
   size_t smem_optin = 0;            // opt-in shared memory per block of the device
   cudaStream_t stream = nullptr;
   bool own_stream = false;
@@ -118,9 +120,7 @@ class Executor {
   size_t stream_smem = 0;
   int stream_half = 0;
   // tensor parallelism: sum over the ranks of a buffer of partial projections, on the executor's stream
-  int tp_rank = 0, tp_world = 1;
   NcclApi::Comm tp_comm = nullptr;
-  void tp_allreduce(float* buf, size_t count);
   unsigned barrier_epoch = 0;
   // chained decode kernel: exchange area (two parity copies of flag-carrying words) and the next free tag
   fu_u64* ll_dev = nullptr;
