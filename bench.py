@@ -154,6 +154,46 @@ class CpuArm:
         return n / (time.perf_counter() - t0)
 
 
+def xnnpack_baseline(rec, cfg, thread_counts) -> dict:
+    """The same CPU sample with the matrix products on XNNPACK's dynamically-quantised int8 fully-connected
+    operator (the XNNPACK build inside torch; not LiteRT).  A timing baseline beside the oracle port, never a
+    parity reference: activations are quantised to int8 per row."""
+    from oracle import oracle as orc
+    out = {"library": "XNNPACK as bundled in torch (qd8-f32-qc8w fully-connected; int4 values held as int8)", "runs": []}
+    try:
+        for th in thread_counts:
+            if not orc.use_xnnpack(th):
+                out["unavailable"] = "XNNPACK symbols could not be bound from libtorch_cpu.so"
+                break
+            arm = CpuArm(rec, cfg)
+            assert arm.ex.prefill(arm.ids[:8]) == 0    # first use creates and packs the operators
+            arm.ex.reset()
+            p = arm.prefill()
+            arm.decode_step(2)
+            d = float(np.mean([arm.decode_step(CPU_DECODE_TOKENS_PER_STEP) for _ in range(3)]))
+            out["runs"].append({"threads": th, "decode_tok_s": d, "prefill_tok_s": p})
+            del arm
+    finally:
+        orc.use_plain_matmul(host_threads())
+    return out
+
+
+def xnnpack_leg(model: str, thread_counts) -> dict:
+    """Runs xnnpack_baseline in a child process: OpenMP's and pthreadpool's workers must not both spin on the
+    same cores, and the wait policy can only be chosen before the OpenMP runtime loads."""
+    import subprocess
+    env = dict(os.environ, OMP_WAIT_POLICY="passive")
+    t0 = time.perf_counter()
+    try:
+        r = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "xnnpack", "--model", model, "--threads",
+                            ",".join(str(t) for t in thread_counts)], env=env, capture_output=True, text=True, timeout=600)
+        out = json.loads(r.stdout.strip().splitlines()[-1])
+    except Exception as e:  # a timing extra: its absence must not fail the arm
+        out = {"unavailable": f"{type(e).__name__}: {e}"[:300]}
+    out["wall_s"] = time.perf_counter() - t0
+    return out
+
+
 def cpu_sample_text(n: int) -> str:
     return (f"CPU oracle port (plain C, OpenMP, all host threads), same weights and seeded prompt: the {PREFILL_TOKENS}-id "
             f"prefill once, then {n} greedy decode steps per bench step at context {PREFILL_TOKENS}+")
@@ -218,6 +258,8 @@ def run_reference(args, rank: int) -> None:
         "gpu_launches": 0, "wall_s": wall,
         "note": "the reference's LiteRT/XNNPACK CPU backend cannot be built here; this is the CPU restatement",
     }
+    if not args.no_xnnpack:
+        line["xnnpack"] = xnnpack_leg(args.model, sorted({cores, min(4, cores)}, reverse=True))
     print(json.dumps(line), flush=True)
 
 
@@ -385,11 +427,13 @@ def main() -> None:
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
     ap.add_argument("--warmup", type=int, default=3)
-    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference", "xnnpack"])
     ap.add_argument("--model", default="gemma3-1b")
     ap.add_argument("--decode-mode", type=int, default=0)
     ap.add_argument("--prefill-gemm", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-xnnpack", action="store_true", help="skip the XNNPACK leg of the CPU arms")
+    ap.add_argument("--threads", default="", help="thread counts of the XNNPACK leg (--impl xnnpack)")
     ap.add_argument("--no-e2e", action="store_true")
     ap.add_argument("--batched-sessions", type=int, default=4,
                     help="extra leg: this many sessions per GPU decoded in lockstep (0 = skip)")
@@ -404,6 +448,12 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "xnnpack":                   # child process of the CPU arms, prints one JSON object
+        if int(os.environ.get("RANK", "0")) == 0:
+            cfg, rec, _ = load_model(args.model)
+            print(json.dumps(xnnpack_baseline(rec, cfg, [int(t) for t in args.threads.split(",") if t] or [host_threads()])),
+                  flush=True)
+        return
     if args.impl == "reference":
         run_reference(args, rank)
         return

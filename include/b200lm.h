@@ -38,8 +38,13 @@ enum {
   B200LM_DECODE_PHASE_KERNELS = 1,     /* one kernel per phase, CUDA graph per step */
   B200LM_DECODE_PERSISTENT = 2,        /* one cooperative kernel, grid barrier per phase, weights streamed by bulk async copies */
   B200LM_DECODE_PERSISTENT_BASIC = 3,  /* one cooperative kernel, grid barrier per phase, plain loads (comparison) */
-  B200LM_DECODE_CHAINED = 4            /* one cooperative kernel without grid barriers: phases hand results over in
+  B200LM_DECODE_CHAINED = 4,           /* one cooperative kernel without grid barriers: phases hand results over in
                                           flag-carrying words, gate/up + down fused */
+  B200LM_DECODE_WIDE = 5               /* lockstep groups of up to 128 sessions: the projections of a step run on the
+                                          tensor-core int4 GEMM of the prefill path with the sessions as its token
+                                          rows (bf16 activations), one attention CTA per (session, kv head), one CUDA
+                                          graph per step.  AUTO picks it when n_sessions > 4.  Needs the tensor-core
+                                          GEMM weights; no tensor parallelism. */
 };
 enum { B200LM_GEMM_AUTO = 0, B200LM_GEMM_CHECK = 1, B200LM_GEMM_TCGEN05 = 2 };
 
@@ -56,8 +61,8 @@ typedef struct B200LmConfig {
                               (page, slot) computation cannot pass the KV indexing checks by
                               accident.  Results do not depend on it. */
   void* stream;            /* cudaStream_t to run on, or NULL for an own stream */
-  int32_t n_sessions;      /* sessions held by this executor, 1..4 (0 = 1); see
-                              B200Lm_DecodeTokensBatch */
+  int32_t n_sessions;      /* sessions held by this executor (0 = 1): 1..4 with the persistent decode
+                              kernels, up to 128 in B200LM_DECODE_WIDE; see B200Lm_DecodeTokensBatch */
   int32_t reserved1;
   /* Tensor parallelism (BASELINE config 5).  tp_world > 1: this executor is rank tp_rank of tp_world and
    * the model image holds THAT RANK'S SHARD (query / kv heads and FFN columns split over the ranks, see
@@ -127,7 +132,8 @@ int B200Lm_DecodeTokens(B200LmExecutor* e, int32_t n_steps, int32_t* out_ids, ch
  * per step for the whole batch; out_ids is [n_steps][n_sessions].  Every
  * session must have a pending id (i.e. have been prefilled).  With three or
  * four sessions the decode activations are quantised to two int8 terms
- * instead of three (relative error 6e-5 instead of 5e-7). */
+ * instead of three (relative error 6e-5 instead of 5e-7); in B200LM_DECODE_WIDE
+ * (more than four sessions) they are bf16, as in prefill. */
 int B200Lm_SelectSession(B200LmExecutor* e, int32_t session, char** err);
 int B200Lm_GetNumSessions(B200LmExecutor* e, int32_t* out, char** err);
 int B200Lm_PrefillSession(B200LmExecutor* e, int32_t session, const int32_t* ids, int32_t n,

@@ -31,7 +31,7 @@ FAILED_PRECONDITION, OUT_OF_RANGE, UNIMPLEMENTED, INTERNAL = 9, 11, 12, 13
 _CODE_NAMES = {0: "OK", 1: "CANCELLED", 3: "INVALID_ARGUMENT", 4: "DEADLINE_EXCEEDED", 5: "NOT_FOUND",
                9: "FAILED_PRECONDITION", 11: "OUT_OF_RANGE", 12: "UNIMPLEMENTED", 13: "INTERNAL"}
 
-DECODE_AUTO, DECODE_PHASE_KERNELS, DECODE_PERSISTENT, DECODE_PERSISTENT_BASIC, DECODE_CHAINED = 0, 1, 2, 3, 4
+DECODE_AUTO, DECODE_PHASE_KERNELS, DECODE_PERSISTENT, DECODE_PERSISTENT_BASIC, DECODE_CHAINED, DECODE_WIDE = 0, 1, 2, 3, 4, 5
 GEMM_AUTO, GEMM_CHECK, GEMM_TCGEN05 = 0, 1, 2
 
 

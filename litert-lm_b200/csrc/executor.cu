@@ -132,6 +132,10 @@ std::shared_ptr<Model> Model::load(const uint8_t* image, size_t n, int device, b
     const TensorEntry& e = qmat("embed", d.vocab, d.d);
     m->embed_rows = upload(*m, bytes(e), (size_t)e.nbytes);
     m->embed_scale = fvec("embed.scale", d.vocab);
+    if (want_tc) {
+      const TensorEntry& es = rec.need("embed.scale", 1);
+      upload_w4g(*m, bytes(e), reinterpret_cast<const float*>(bytes(es)), d.vocab, d.d, &m->head_g, &m->head_gs);
+    }
     auto ht = w4t_host(bytes(e), d.vocab, d.d, [](int64_t r) { return r; });
     m->head_w = reinterpret_cast<const uint4*>(upload(*m, ht.data(), ht.size()));
     m->head_ws = upload_w4ts(*m, ht, reinterpret_cast<const float*>(bytes(rec.need("embed.scale", 1))), d.vocab, d.d);
@@ -395,6 +399,7 @@ Executor::~Executor() {
   cudaSetDevice(device);
   if (stream) cudaStreamSynchronize(stream);
   if (graph_exec) cudaGraphExecDestroy(graph_exec);
+  for (auto& g : wide_graphs) cudaGraphExecDestroy(g.second);
   if (tp_comm) {
     try { NcclApi::get().CommDestroy(tp_comm); } catch (...) {}
   }
@@ -450,17 +455,26 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   B2_CHECK(e->prefill_gemm != B200LM_GEMM_TCGEN05 || model->has_tc, kFailedPrecondition,
            "tensor-core GEMM weights were not loaded for this model");
   B2_CHECK(cfg.page_order == 0 || cfg.page_order == 1, kInvalidArgument, "page_order must be 0 or 1");
-  B2_CHECK(cfg.decode_mode >= B200LM_DECODE_AUTO && cfg.decode_mode <= B200LM_DECODE_CHAINED, kInvalidArgument,
+  B2_CHECK(cfg.decode_mode >= B200LM_DECODE_AUTO && cfg.decode_mode <= B200LM_DECODE_WIDE, kInvalidArgument,
            "decode_mode must be one of B200LM_DECODE_*");
   e->decode_mode = cfg.decode_mode == B200LM_DECODE_AUTO ? B200LM_DECODE_CHAINED : cfg.decode_mode;
+  // more sessions than the GEMV kernels carry per step: the projections run on the tensor-core GEMM
+  if (cfg.n_sessions > kMaxCols && cfg.decode_mode == B200LM_DECODE_AUTO) e->decode_mode = B200LM_DECODE_WIDE;
+  if (e->decode_mode == B200LM_DECODE_WIDE)
+    B2_CHECK(e->prefill_gemm == B200LM_GEMM_TCGEN05 && cfg.tp_world <= 1, kFailedPrecondition,
+             "the wide decode mode needs the tensor-core GEMM weights and no tensor parallelism");
   // a collective cannot run inside a persistent kernel: tensor-parallel decode is one kernel per phase
   if (cfg.tp_world > 1) e->decode_mode = B200LM_DECODE_PHASE_KERNELS;
   const int esz = d.kv_dtype == 0 ? 4 : 2;
   // ---- paged KV cache
   e->pages_per_seq = (e->max_num_tokens + kPage - 1) / kPage;     // the cache holds max_num_tokens positions per session
   e->n_sessions = cfg.n_sessions > 0 ? cfg.n_sessions : 1;
-  B2_CHECK(e->n_sessions <= kMaxCols, kInvalidArgument,
-           "n_sessions exceeds the " + std::to_string(kMaxCols) + " sessions one decode step can carry");
+  {
+    const int cap = e->decode_mode == B200LM_DECODE_WIDE ? kWideMax : kMaxCols;
+    B2_CHECK(e->n_sessions <= cap, kInvalidArgument,
+             "n_sessions exceeds the " + std::to_string(cap) + " sessions one decode step of this mode can carry");
+  }
+  const int max_cols = std::max(kMaxCols, e->n_sessions);
   e->parked.resize(e->n_sessions);
   const int total_pages = e->pages_per_seq * e->n_sessions;
   size_t pool = (size_t)total_pages * d.hkv * kPage * d.hd;
@@ -540,14 +554,19 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   a.opart = reinterpret_cast<float*>(e->alloc(sizeof(float) * a.o_slices * kMaxCols * d.d, true));
   a.act = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.ffn, true));
   a.fpart = reinterpret_cast<float*>(e->alloc(sizeof(float) * a.down_slices * kMaxCols * d.d, true));
-  a.logits = reinterpret_cast<float*>(e->alloc(sizeof(float) * kMaxCols * d.vocab, true));
+  a.logits = reinterpret_cast<float*>(e->alloc(sizeof(float) * max_cols * d.vocab, true));
   a.amax_val = reinterpret_cast<float*>(e->alloc(sizeof(float) * e->n_sms * kMaxCols, true));
   a.amax_idx = reinterpret_cast<int*>(e->alloc(sizeof(int) * e->n_sms * kMaxCols, true));
   a.step_capacity = d.max_ctx;
-  a.step_tokens = reinterpret_cast<int*>(e->alloc(sizeof(int) * a.step_capacity * kMaxCols, true));
+  a.step_tokens = reinterpret_cast<int*>(e->alloc(sizeof(int) * a.step_capacity * max_cols, true));
+  if (e->decode_mode == B200LM_DECODE_WIDE) {
+    int* ws = reinterpret_cast<int*>(e->alloc(sizeof(int) * 3 * kWideMax, true));
+    e->wide = WideState{ws, ws + kWideMax, ws + 2 * kWideMax};
+  }
   a.advance = 1;
   // the one-kernel-per-phase fallback drives one session; the persistent kernels carry all of them
-  e->dec_smem = dec_smem_bytes(d, (e->decode_mode == B200LM_DECODE_PERSISTENT || e->decode_mode == B200LM_DECODE_CHAINED) ? 1 : e->n_sessions);
+  e->dec_smem = dec_smem_bytes(d, e->decode_mode == B200LM_DECODE_PHASE_KERNELS || e->decode_mode == B200LM_DECODE_PERSISTENT_BASIC
+                                      ? e->n_sessions : 1);
   B2_CHECK(e->dec_smem <= (size_t)prop.sharedMemPerBlockOptin, kUnimplemented,
            "decode kernels need more shared memory than the device offers");
   raise_dyn_smem(decode_phase_kernel, (size_t)(e->dec_smem));
@@ -642,12 +661,13 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
     e->tm_act = make_activation_map(e->pf_act, (int)tp, d.ffn);
   }
   // page-locked staging: logits | kTokRing slices of prompt ids | sampled ids of a decode call | state words
-  size_t pin = sizeof(float) * (size_t)d.vocab + sizeof(int) * (kTokRing * tp + (size_t)d.max_ctx * kMaxCols) + 4096;
+  size_t pin = sizeof(float) * (size_t)d.vocab + sizeof(int) * (kTokRing * tp + (size_t)d.max_ctx * max_cols + 3 * kWideMax) + 4096;
   B2_CUDA(cudaMallocHost(&e->pinned, pin));
   e->pin_logits = reinterpret_cast<float*>(e->pinned);
   e->pin_ints = reinterpret_cast<int*>(e->pin_logits + d.vocab);
   e->pin_steps = e->pin_ints + (size_t)kTokRing * tp;
-  e->pin_state = reinterpret_cast<DecodeState*>(e->pin_steps + (size_t)d.max_ctx * kMaxCols);
+  e->pin_wide = e->pin_steps + (size_t)d.max_ctx * max_cols;
+  e->pin_state = reinterpret_cast<DecodeState*>(e->pin_wide + 3 * kWideMax);
   for (int i = 0; i < kTokRing; ++i) B2_CUDA(cudaEventCreateWithFlags(&e->tok_ring_done[i], cudaEventDisableTiming));
   B2_CUDA(cudaDeviceSynchronize());
   return e;
@@ -906,6 +926,10 @@ void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
   const ModelDims& d = model->dims;
   const int ncta = n_sms;
   if (first_session < 0) first_session = active;
+  if (decode_mode == B200LM_DECODE_WIDE) {
+    launch_wide_steps(nsteps, ncols, first_session);
+    return;
+  }
   if (decode_mode == B200LM_DECODE_CHAINED) {
     DecodeArgs a = dargs;
     a.ncols = ncols;
@@ -1007,7 +1031,113 @@ void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
   launches += (int64_t)nsteps * (5 * d.n_layers + 2);
 }
 
+// One wide step for sessions [first, first + nb): the token rows of the GEMMs are the sessions.
+void Executor::wide_step(int nb, int first) {
+  const ModelDims& d = model->dims;
+  int* err = &dargs.st->err;
+  const int mode = B200LM_GEMM_TCGEN05;
+  const size_t attn_smem = sizeof(float) * ((size_t)(d.group() + 2) * d.hd + (size_t)8 * d.group() * (d.hd + 2));
+  pf_embed_norm_kernel<<<nb, kPfThreads, sizeof(float) * d.d, stream>>>(wide.tok, model->embed_rows, model->embed_scale,
+                                                                        model->layers_host[0].g_pre_attn, d.d, d.vocab, d.eps,
+                                                                        pf_xres, pf_h, err);
+  int64_t* nl = &launches;
+  ++*nl;
+  for (int li = 0; li < d.n_layers; ++li) {
+    const LayerWeights& L = model->layers_host[li];
+    const LayerGemmWeights& Gm = model->gemm_host[li];
+    // split K so that the few token rows still spread the weight tiles over the SMs; the attention reads whole rows
+    int ks_q = pick_ksplit(nb, (d.nqkv() + kTsRows - 1) / kTsRows, d.d / 64, n_sms);
+    if ((size_t)ks_q * d.nqkv() > (size_t)8 * d.d) ks_q = 1;
+    launch_gemm(stream, mode, tm_h, pf_h, L.wqkv, L.sqkv, Gm.wqkv, Gm.sqkv, nb, d.nqkv(), d.d, ks_q, false,
+                ks_q > 1 ? pf_parts : pf_qkv, nullptr, err, nl);
+    if (ks_q > 1) {
+      const size_t count = (size_t)nb * d.nqkv();
+      wide_sum_parts_kernel<<<(unsigned)((count / 4 + 255) / 256), 256, 0, stream>>>(pf_parts, ks_q, count, count, pf_qkv);
+      ++*nl;
+    }
+    AttnJob j;
+    memset(&j, 0, sizeof j);
+    j.qkv = pf_qkv;
+    j.pos = wide.pos;
+    j.page_table = page_table_dev + (size_t)first * pages_per_seq;
+    j.pages_per_seq = pages_per_seq;
+    j.seq_stride = 1;
+    j.is_global = L.is_global;
+    j.nsplit = 1;
+    j.appended = 0;                                 // the kernel norms, rotates and appends this step's K / V rows
+    j.g_q = L.g_q;
+    j.g_k = L.g_k;
+    j.cosT = model->rope_cos[L.is_global];
+    j.sinT = model->rope_sin[L.is_global];
+    j.kv = kv_host[li];
+    j.out_bf16 = pf_attn;
+    j.err = err;
+    pf_attn_kernel<<<nb * d.hkv, 256, attn_smem, stream>>>(d, j);
+    ++*nl;
+    const int ks_o = pick_ksplit(nb, (d.d + kTsRows - 1) / kTsRows, d.nq() / 64, n_sms);
+    launch_gemm(stream, mode, tm_attn, pf_attn, L.wo, L.so, Gm.wo, Gm.so, nb, d.d, d.nq(), ks_o, false, pf_parts, nullptr, err, nl);
+    launch_resid_norm(stream, pf_parts, ks_o, nb, d, L.g_post_attn, L.g_pre_ffn, pf_xres, pf_h);
+    ++*nl;
+    launch_gemm(stream, mode, tm_h, pf_h, L.wgu, L.sgu, Gm.wgu, Gm.sgu, nb, 2 * d.ffn, d.d, 1, true, nullptr, pf_act, err, nl);
+    const int ks_d = pick_ksplit(nb, (d.d + kTsRows - 1) / kTsRows, d.ffn / 64, n_sms);
+    launch_gemm(stream, mode, tm_act, pf_act, L.wdown, L.sdown, Gm.wdown, Gm.sdown, nb, d.d, d.ffn, ks_d, false, pf_parts, nullptr,
+                err, nl);
+    const float* g_next = li + 1 < d.n_layers ? model->layers_host[li + 1].g_pre_attn : model->g_final;
+    launch_resid_norm(stream, pf_parts, ks_d, nb, d, L.g_post_ffn, g_next, pf_xres, pf_h);
+    ++*nl;
+  }
+  launch_gemm(stream, mode, tm_h, pf_h, nullptr, nullptr, model->head_g, model->head_gs, nb, d.vocab, d.d, 1, false, dargs.logits,
+              nullptr, err, nl);
+  wide_argmax_kernel<<<nb, kWideArgThreads, 0, stream>>>(dargs.logits, d.vocab, nb, wide, dargs.step_tokens);
+  ++*nl;
+  B2_CUDA(cudaGetLastError());
+}
+
+void Executor::launch_wide_steps(int nsteps, int nb, int first) {
+  B2_CHECK(nb >= 1 && nb <= kWideMax && first >= 0 && first + nb <= n_sessions, kInternal, "wide step outside the sessions");
+  B2_CHECK(model->head_g != nullptr, kFailedPrecondition, "the wide decode mode needs the tensor-core GEMM weights");
+  if (nsteps == 1) {                                 // a single step is not worth a capture
+    wide_step(nb, first);
+    return;
+  }
+  auto key = std::make_pair(nb, first);
+  auto it = wide_graphs.find(key);
+  if (it == wide_graphs.end()) {
+    const int64_t before = launches;
+    cudaGraph_t graph;
+    B2_CUDA(cudaStreamBeginCapture(stream, cudaStreamCaptureModeThreadLocal));
+    try {
+      wide_step(nb, first);
+    } catch (...) {
+      cudaGraph_t dead = nullptr;
+      cudaStreamEndCapture(stream, &dead);
+      if (dead) cudaGraphDestroy(dead);
+      throw;
+    }
+    B2_CUDA(cudaStreamEndCapture(stream, &graph));
+    cudaGraphExec_t exec = nullptr;
+    B2_CUDA(cudaGraphInstantiate(&exec, graph, 0));
+    cudaGraphDestroy(graph);
+    wide_per_step = launches - before;
+    launches = before;
+    it = wide_graphs.emplace(key, exec).first;
+  }
+  for (int s = 0; s < nsteps; ++s) B2_CUDA(cudaGraphLaunch(it->second, stream));
+  launches += (int64_t)nsteps * wide_per_step;
+}
+
 void Executor::push_decode_state(const int* tokens, const int* pos, int ncols) {
+  if (decode_mode == B200LM_DECODE_WIDE) {
+    B2_CUDA(cudaStreamSynchronize(stream));        // the staging words of the previous call have been read
+    for (int c = 0; c < ncols; ++c) {
+      pin_wide[c] = tokens[c];
+      pin_wide[kWideMax + c] = pos[c];
+      pin_wide[2 * kWideMax + c] = pos[c];
+    }
+    B2_CUDA(cudaMemcpyAsync(wide.tok, pin_wide, sizeof(int) * 3 * kWideMax, cudaMemcpyHostToDevice, stream));
+    h2d_bytes += 2 * sizeof(int) * (size_t)ncols;
+    return;
+  }
   DecodeState* ps = pin_state;
   memset(ps, 0, sizeof(DecodeState));
   for (int c = 0; c < ncols; ++c) {
@@ -1072,7 +1202,7 @@ void Executor::decode_tokens_batch(int nsteps, int* out_ids) {
   B2_CHECK(nsteps > 0, kInvalidArgument, "n_steps must be positive");
   B2_CUDA(cudaSetDevice(device));
   const int keep = active;
-  int tok[kMaxCols], pos[kMaxCols];
+  std::vector<int> tok(n_sessions), pos(n_sessions);
   for (int sn = 0; sn < n_sessions; ++sn) {        // validate every session before any state changes
     const int pending = sn == active ? next_input_token : parked[sn].next_input_token;
     const int step = sn == active ? current_step : parked[sn].current_step;
@@ -1084,7 +1214,7 @@ void Executor::decode_tokens_batch(int nsteps, int* out_ids) {
     tok[sn] = take_decode_id(nullptr);
     pos[sn] = current_step;
   }
-  push_decode_state(tok, pos, n_sessions);
+  push_decode_state(tok.data(), pos.data(), n_sessions);
   launch_decode_steps(nsteps, n_sessions, 0);
   int* dst = pin_steps;
   B2_CUDA(cudaMemcpyAsync(dst, dargs.step_tokens, sizeof(int) * (size_t)nsteps * n_sessions, cudaMemcpyDeviceToHost,

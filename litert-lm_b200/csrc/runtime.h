@@ -3,6 +3,7 @@
 #include <cuda.h>
 #include <cuda_runtime.h>
 
+#include <map>
 #include <memory>
 #include <utility>
 #include <vector>
@@ -11,6 +12,7 @@
 #include "common.cuh"
 #include "decode_ops.cuh"
 #include "decode_fused.cuh"
+#include "decode_wide.cuh"
 #include "tp_nccl.h"
 
 namespace b200lm {
@@ -30,6 +32,8 @@ struct Model {
   const uint8_t* embed_rows = nullptr;
   const float* embed_scale = nullptr;
   const uint4* head_w = nullptr;
+  const uint8_t* head_g = nullptr;   // the head in the tensor-core GEMM's layout (wide decode), with has_tc
+  const float* head_gs = nullptr;
   const float* g_final = nullptr;
   float gmax_final = 0.f;
   const float* rope_cos[2] = {nullptr, nullptr};
@@ -131,6 +135,13 @@ class Executor {
   bool chained_ok = false;          // the model fits the chained kernel (with n_sessions columns)
   long long* trace_dev = nullptr;
   cudaGraphExec_t graph_exec = nullptr;
+  // wide lockstep decode (B200LM_DECODE_WIDE)
+  WideState wide{nullptr, nullptr, nullptr};
+  int* pin_wide = nullptr;          // staging of the wide state words
+  std::map<std::pair<int, int>, cudaGraphExec_t> wide_graphs;   // one step, keyed by (sessions, first session)
+  int64_t wide_per_step = 0;        // kernel launches of one wide step
+  void wide_step(int nb, int first);
+  void launch_wide_steps(int nsteps, int nb, int first);
   // prefill scratch
   int t_max = 0, t_pad = 0;
   int* pf_tokens = nullptr;

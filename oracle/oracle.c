@@ -332,10 +332,24 @@ void orc_model_cfg(const OrcModel* m, int32_t* out16) {
   memcpy(out16, v, sizeof v);
 }
 
+/* Optional replacement of the matrix product (the XNNPACK timing baseline of xnn_baseline.c installs one);
+ * the parity oracle never sets it.  A non-zero return falls back to the loop below. */
+typedef int (*OrcMatmulHook)(const void* key, const int8_t* w, const float* scale, int N, int K, const float* x, int T,
+                             float* y, int ldy);
+static OrcMatmulHook g_matmul_hook = NULL;
+void orc_set_matmul_hook(void* fn) { g_matmul_hook = (OrcMatmulHook)fn; }
+#ifdef _OPENMP
+#include <omp.h>
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+#else
+void orc_set_threads(int n) { (void)n; }
+#endif
+
 /* y[t][n] = scale[n] * sum_k W[n][k] x[t][k].  fp32 products are summed in
  * 32-element chunks in fp32 and the chunk totals in double. */
 static void matmul_w4(const OrcMat* m, const float* x, int T, float* y, int ldy) {
   int N = m->rows, K = m->cols;
+  if (g_matmul_hook && g_matmul_hook(m->w, m->w, m->scale, N, K, x, T, y, ldy) == 0) return;
 #pragma omp parallel for schedule(static)
   for (int n = 0; n < N; ++n) {
     const int8_t* w = m->w + (size_t)n * K;

@@ -24,6 +24,43 @@ def build(force: bool = False) -> str:
     return _LIB_PATH
 
 
+_xnnb = None
+
+
+def use_xnnpack(threads: int) -> bool:
+    """Timing baseline only: routes the oracle's matrix products through XNNPACK's int4-weight /
+    dynamically-quantised-int8-activation fully-connected operator (the XNNPACK build inside torch) on a pool
+    of `threads` workers, and limits the OpenMP parts to the same count.  False when it cannot be set up."""
+    global _xnnb
+    try:
+        import torch  # noqa: F401  (loads libtorch_cpu.so, which exports the xnn_* symbols)
+        inc = os.path.join(os.path.dirname(torch.__file__), "include")
+        out = os.path.join(_HERE, "libxnnb.so")
+        src = os.path.join(_HERE, "xnn_baseline.c")
+        if not os.path.exists(out) or os.path.getmtime(out) < os.path.getmtime(src):
+            subprocess.check_call(["make", "-C", _HERE, "-B", "libxnnb.so", f"TORCH_INC={inc}"], stdout=subprocess.DEVNULL,
+                                  stderr=subprocess.DEVNULL)
+        if _xnnb is None:
+            _xnnb = C.CDLL(out, mode=C.RTLD_GLOBAL)
+            _xnnb.xnnb_init.argtypes = [C.c_int, C.c_char_p]
+            _xnnb.xnnb_init.restype = C.c_int
+        cpu_lib = os.path.join(os.path.dirname(torch.__file__), "lib", "libtorch_cpu.so")
+        if _xnnb.xnnb_init(int(threads), cpu_lib.encode()) != 0:
+            return False
+        lib().orc_set_matmul_hook(C.cast(_xnnb.xnnb_matmul, C.c_void_p))
+        lib().orc_set_threads(int(threads))
+        return True
+    except Exception:
+        return False
+
+
+def use_plain_matmul(threads: int = 0) -> None:
+    """Back to the oracle's own matrix product (the parity configuration)."""
+    lib().orc_set_matmul_hook(None)
+    if threads:
+        lib().orc_set_threads(int(threads))
+
+
 def lib() -> C.CDLL:
     global _lib
     if _lib is None:
@@ -57,6 +94,8 @@ def lib() -> C.CDLL:
             "orc_exec_read_kv": (None, [vp, C.c_int, C.c_int, C.c_int, C.c_int, vp]),
             "orc_matmul_w4": (None, [vp, vp, C.c_int, C.c_int, vp, C.c_int, vp]),
             "orc_attention": (None, [vp, vp, vp] + [C.c_int] * 7 + [vp]),
+            "orc_set_matmul_hook": (None, [vp]),
+            "orc_set_threads": (None, [C.c_int]),
         }
         for name, (res, args) in sig.items():
             fn = getattr(L, name)
