@@ -272,14 +272,17 @@ def run_cfg4(args, pkg, cfg, img, stream, rank: int, world: int, local_rank: int
     import torch.distributed as dist
     mine = pkg.sharding.shard_sessions(args.sessions, world, rank)
     cap = PREFILL_TOKENS + DECODE_STEPS + 256
-    owner, group = None, 4
-    while owner is None:
+    # the largest lockstep group first: all of this GPU's sessions in one wide group (tensor-core GEMM decode),
+    # then what the persistent GEMV kernels carry
+    owner, group = None, 0
+    for group in ([args.group] if args.group > 0 else []) + [min(len(mine), 128), 4, 2, 1]:
         try:
             owner = pkg.B200LlmExecutor(img, device=local_rank, stream=stream.cuda_stream, n_sessions=group, max_num_tokens=cap)
+            break
         except pkg.StatusError:
             if group == 1:
                 raise
-            group //= 2
+    decode_mode = owner.GetDecodeMode()
     groups = [mine[i:i + group] for i in range(0, len(mine), group)]
     execs = [owner]
     for g in groups[1:]:
@@ -337,10 +340,14 @@ def run_cfg4(args, pkg, cfg, img, stream, rank: int, world: int, local_rank: int
         "metric": "aggregate decode tok/s, 64 concurrent sessions (1024-token prompt + 256 greedy steps each), Gemma3-4B-shaped int4",
         "value": tok / (dec_ms / 1e3), "unit": "tok/s", "n_gpus": world, "steps": n, "warmup": 1,
         "ms_per_step": (pf_ms + dec_ms) / n, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-        "dtype": "int4 weights; int8 activation terms (decode), bf16 MMA (prefill), fp32 accumulate", "data": "synthetic",
+        "dtype": ("int4 weights; bf16 activations on the tensor-core GEMM (prefill and wide decode), fp32 accumulate"
+                  if decode_mode == pkg.DECODE_WIDE else
+                  "int4 weights; int8 activation terms (decode), bf16 MMA (prefill), fp32 accumulate"), "data": "synthetic",
         "config": {"workload": f"{cfg.name}: {args.sessions} sessions x ({PREFILL_TOKENS}-token prefill + {DECODE_STEPS} decode steps), "
                                f"sharded over {world} GPU(s), no collective", "seed": cfg.seed, "sessions_per_gpu": len(mine),
-                   "lockstep_group": group, "kv_cache": "fp32" if cfg.kv_dtype == 0 else "bf16", "context": cfg.max_ctx,
+                   "lockstep_group": group, "decode_mode": {pkg.DECODE_WIDE: "wide (tensor-core GEMM per step, CUDA graph)",
+                                                            pkg.DECODE_CHAINED: "chained persistent kernel"}.get(decode_mode, str(decode_mode)),
+                   "kv_cache": "fp32" if cfg.kv_dtype == 0 else "bf16", "context": cfg.max_ctx,
                    "kv_capacity_per_session": cap},
         "prefill": {"value": world * n * len(mine) * PREFILL_TOKENS / (pf_ms / 1e3), "unit": "tok/s"},
         "decode_ms_per_group_step": dec_ms / steps_per_gpu,
@@ -441,6 +448,7 @@ def main() -> None:
                     help="cfg2: the headline protocol (default); cfg4: 64 concurrent sessions of the 4B shape, sharded over the GPUs; "
                          "cfg5: tensor parallelism over the GPUs at the 27B shape's layer geometry")
     ap.add_argument("--sessions", type=int, default=64, help="cfg4: concurrent sessions over all GPUs")
+    ap.add_argument("--group", type=int, default=0, help="cfg4: sessions per lockstep group (0 = all of a GPU's sessions, at most 128)")
     ap.add_argument("--decode-steps", type=int, default=DECODE_STEPS,
                     help="decode steps per bench step (256 is the protocol; fewer only for profiler captures)")
     args = ap.parse_args()

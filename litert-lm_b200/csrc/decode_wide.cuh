@@ -7,12 +7,14 @@
 // This file holds the two small kernels the step adds to the prefill kernels; the step itself is
 // Executor::launch_wide_steps.
 #pragma once
+#include "decode_ops.cuh"
 #include "prefill_ops.cuh"
 
 namespace b200lm {
 
 constexpr int kWideMax = 128;          // sessions of one wide step (half a token tile of the GEMM)
 constexpr int kWideArgThreads = 1024;
+constexpr int kWideMaxSplits = 8;     // key splits of one (session, kv head) in the wide attention
 
 // Per-session state of a wide run, device resident: [0, n) token of the next step, [kWideMax, +n)
 // its position, [2 kWideMax, +n) the position of the run's first step.
@@ -67,6 +69,261 @@ wide_argmax_kernel(const float* __restrict__ logits, int vocab, int n, WideState
       st.tok[row] = bi;
       st.pos[row] = p + 1;
     }
+  }
+}
+
+// ------------------------------------------------------------------ attention of a wide step
+// One CTA per (session, kv head, key split).  The session's K / V rows of this head are contiguous inside
+// a page ([page][kv head][slot][hd]), so the CTA streams them in blocks of kWaChunk consecutive positions
+// with one bulk async copy each for K and V into a ring of shared-memory stages, several blocks in flight;
+// the eight warps take two keys of a block each (online softmax per warp, all G query heads of the group
+// together) and the per-warp states are merged at the end.  Split 0 also norms, rotates and appends this
+// step's own K / V row; the current position's row is taken from shared memory, not from the cache.
+constexpr int kWaThreads = 256, kWaWarps = 8, kWaChunk = 2 * kWaWarps, kWaMaxStages = 6;
+
+struct WideAttnArgs {
+  const float* qkv;          // [sessions][nqkv] raw projections of this step
+  const int* pos;            // [sessions] position of this step's token
+  const int* page_table;     // first session's row; rows of pages_per_seq entries
+  int pages_per_seq;
+  int is_global;
+  int nsplit;
+  int stages;                // ring depth (2 .. kWaMaxStages), sized by the host to the shared memory
+  const float *g_q, *g_k, *cosT, *sinT;
+  LayerKv kv;
+  float* part;               // nsplit > 1: [session][kv head][split][G][hd + 2] (o, then m and l)
+  __nv_bfloat16* out;        // nsplit == 1: [session][hq * hd]
+  int* err;
+};
+
+template <typename T, int HD>
+__host__ __device__ constexpr int wa_stage_bytes() { return 2 * kWaChunk * HD * (int)sizeof(T); }
+__host__ __device__ inline size_t wa_fixed_bytes(int hd, int G) {
+  return sizeof(float) * ((size_t)(G + 2) * hd + (size_t)kWaWarps * G * (hd + 2)) + 16 * kWaMaxStages + 128;
+}
+
+template <typename T, int HD, int G>
+__global__ void __launch_bounds__(kWaThreads, 1)
+wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
+  constexpr int VEC = HD / 32, half = HD / 2;
+  constexpr int kStage = wa_stage_bytes<T, HD>();
+  extern __shared__ __align__(128) unsigned char wa_sm[];
+  const int S = a.stages;
+  unsigned char* ring = wa_sm;
+  float* q_s = reinterpret_cast<float*>(wa_sm + (size_t)S * kStage);   // [G][HD]
+  float* k_s = q_s + G * HD;                                           // [HD]
+  float* v_s = k_s + HD;                                               // [HD]
+  float* wm = v_s + HD;                                                // [warps][G]
+  float* wl = wm + kWaWarps * G;
+  float* wo = wl + kWaWarps * G;                                       // [warps][G][HD]
+  uint64_t* full = reinterpret_cast<uint64_t*>(wo + kWaWarps * G * HD);
+  uint64_t* empty = full + kWaMaxStages;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int split = blockIdx.x % a.nsplit;
+  const int kvh = (blockIdx.x / a.nsplit) % dm.hkv;
+  const int qi = blockIdx.x / (a.nsplit * dm.hkv);
+  int pos = a.pos[qi];
+  if (pos < 0 || pos >= dm.max_ctx) {
+    if (threadIdx.x == 0) atomicExch(a.err, (int)kDevBadPosition);
+    pos = 0;
+  }
+  const int* ptab = a.page_table + (size_t)qi * a.pages_per_seq;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kWaWarps); }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  const T* kbase = reinterpret_cast<const T*>(a.kv.k);
+  const T* vbase = reinterpret_cast<const T*>(a.kv.v);
+  // ---- key range of this split; the current position is served from shared memory.  The first blocks are
+  // requested before the prologue below (they depend on the position only), so their latency hides behind it.
+  int k0, k1;
+  attn_split_range(dm, pos, a.is_global, a.nsplit, split, &k0, &k1);
+  const bool has_cur = k1 == pos + 1 && k1 > k0;
+  const int k1s = has_cur ? pos : k1;                  // streamed keys: [k0, k1s)
+  const int cb0 = k0 / kWaChunk;
+  const int nchunks = k1s > k0 ? (k1s + kWaChunk - 1) / kWaChunk - cb0 : 0;
+  auto issue = [&](int c) {                            // thread 0: block c of this split into its stage
+    const int s = c % S, key = (cb0 + c) * kWaChunk;
+    const size_t off = (((size_t)ptab[key / kPage] * dm.hkv + kvh) * kPage + (key % kPage)) * HD;
+    unsigned char* dst = ring + (size_t)s * kStage;
+    mbar_arrive_expect_tx(&full[s], (uint32_t)kStage);
+    bulk_load_1d(dst, kbase + off, kStage / 2, &full[s]);
+    bulk_load_1d(dst + kStage / 2, vbase + off, kStage / 2, &full[s]);
+  };
+  if (threadIdx.x == 0)
+    for (int c = 0; c < nchunks && c < S - 1; ++c) issue(c);
+  // ---- this step's q heads (normed, rotated, scaled), k head and v head
+  const float* row = a.qkv + (size_t)qi * dm.nqkv();
+  const float att_scale = rsqrtf((float)HD);
+  for (int h = warp; h < G + 2; h += kWaWarps) {
+    if (h <= G) {
+      const float* src = h < G ? row + (size_t)(kvh * G + h) * HD : row + dm.nq() + (size_t)kvh * HD;
+      const float* gain = h < G ? a.g_q : a.g_k;
+      float* dst = h < G ? q_s + h * HD : k_s;
+      float ss = 0.f;
+      for (int e = lane; e < HD; e += 32) { const float v = src[e]; ss += v * v; }
+      ss = warp_sum(ss);
+      const float r = rsqrtf(ss / (float)HD + dm.eps);
+      const float post = h < G ? att_scale : 1.0f;
+      for (int e = lane; e < half; e += 32) {
+        const float a0 = src[e] * r * gain[e], b0 = src[e + half] * r * gain[e + half];
+        const float cs = a.cosT[(size_t)pos * half + e], sn = a.sinT[(size_t)pos * half + e];
+        dst[e] = (a0 * cs - b0 * sn) * post;
+        dst[e + half] = (b0 * cs + a0 * sn) * post;
+      }
+    } else {
+      const float* src = row + dm.nq() + dm.nkv() + (size_t)kvh * HD;
+      for (int e = lane; e < HD; e += 32) v_s[e] = src[e];
+    }
+  }
+  __syncthreads();
+  if (split == 0) {          // append: exactly one CTA per (session, kv head)
+    const int page = ptab[pos / kPage], slot = pos % kPage;
+    const size_t off = (((size_t)page * dm.hkv + kvh) * kPage + slot) * HD;
+    T* kw = reinterpret_cast<T*>(a.kv.k);
+    T* vw = reinterpret_cast<T*>(a.kv.v);
+    for (int e = threadIdx.x; e < HD; e += kWaThreads) {
+      if constexpr (sizeof(T) == 4) {
+        kw[off + e] = k_s[e];
+        vw[off + e] = v_s[e];
+        if (a.kv.k16) a.kv.k16[off + e] = __float2bfloat16(k_s[e]);
+      } else {
+        kw[off + e] = __float2bfloat16(k_s[e]);
+        vw[off + e] = __float2bfloat16(v_s[e]);
+      }
+      if (a.kv.v16) a.kv.v16[(((size_t)page * dm.hkv + kvh) * HD + e) * kPage + slot] = __float2bfloat16(v_s[e]);
+    }
+    asm volatile("fence.proxy.async.global;" ::: "memory");     // later steps fetch these rows with bulk copies
+  }
+  float q[G][VEC], o[G][VEC], m[G], l[G];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    m[g] = -INFINITY;
+    l[g] = 0.f;
+#pragma unroll
+    for (int c = 0; c < VEC; ++c) {
+      q[g][c] = q_s[g * HD + head_elem<HD>(lane, c)];
+      o[g][c] = 0.f;
+    }
+  }
+  bool ok = true;
+  for (int c = 0; c < nchunks && ok; ++c) {
+    const int s = c % S;
+    if (threadIdx.x == 0 && c + S - 1 < nchunks) {     // refill the stage that block c - 1 used
+      const int cn = c + S - 1;
+      if (cn >= S) ok = mbar_wait(&empty[cn % S], (uint32_t)((cn / S - 1) & 1), a.err);
+      if (ok) issue(cn);
+    }
+    ok = __shfl_sync(0xffffffffu, (int)ok, 0) != 0;    // warp 0 follows its producer lane; the others see the error word
+    if (!ok) break;
+    ok = mbar_wait(&full[s], (uint32_t)((c / S) & 1), a.err);
+    if (!ok) break;
+    const T* ks = reinterpret_cast<const T*>(ring + (size_t)s * kStage);
+    const T* vs = ks + kWaChunk * HD;
+    const int ka = (cb0 + c) * kWaChunk + warp, kb = ka + kWaWarps;
+    const bool hasa = ka >= k0 && ka < k1s, hasb = kb >= k0 && kb < k1s;
+    float kA[VEC], kB[VEC], vA[VEC], vB[VEC];
+    load_head_row_smem<T, HD>(ks + (size_t)warp * HD, lane, kA);
+    load_head_row_smem<T, HD>(ks + (size_t)(warp + kWaWarps) * HD, lane, kB);
+    load_head_row_smem<T, HD>(vs + (size_t)warp * HD, lane, vA);
+    load_head_row_smem<T, HD>(vs + (size_t)(warp + kWaWarps) * HD, lane, vB);
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&empty[s]);             // rows are in registers
+    if (hasa || hasb) {
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float sa = 0.f, sb = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < VEC; ++cc) { sa += q[g][cc] * kA[cc]; sb += q[g][cc] * kB[cc]; }
+        sa = hasa ? warp_sum(sa) : -INFINITY;
+        sb = hasb ? warp_sum(sb) : -INFINITY;
+        const float mn = fmaxf(m[g], fmaxf(sa, sb));
+        const float corr = __expf(m[g] - mn);
+        const float pa = hasa ? __expf(sa - mn) : 0.f, pb = hasb ? __expf(sb - mn) : 0.f;
+        l[g] = l[g] * corr + pa + pb;
+        m[g] = mn;
+#pragma unroll
+        for (int cc = 0; cc < VEC; ++cc) o[g][cc] = o[g][cc] * corr + (hasa ? pa * vA[cc] : 0.f) + (hasb ? pb * vB[cc] : 0.f);
+      }
+    }
+  }
+  if (has_cur && warp == 0) {                          // this step's own key
+    float kA[VEC], vA[VEC];
+#pragma unroll
+    for (int cc = 0; cc < VEC; ++cc) {
+      kA[cc] = k_s[head_elem<HD>(lane, cc)];
+      vA[cc] = v_s[head_elem<HD>(lane, cc)];
+      if constexpr (sizeof(T) == 2) {                  // what a bf16 cache hands back
+        kA[cc] = __bfloat162float(__float2bfloat16(kA[cc]));
+        vA[cc] = __bfloat162float(__float2bfloat16(vA[cc]));
+      }
+    }
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float sa = 0.f;
+#pragma unroll
+      for (int cc = 0; cc < VEC; ++cc) sa += q[g][cc] * kA[cc];
+      sa = warp_sum(sa);
+      const float mn = fmaxf(m[g], sa);
+      const float corr = __expf(m[g] - mn), pa = __expf(sa - mn);
+      l[g] = l[g] * corr + pa;
+      m[g] = mn;
+#pragma unroll
+      for (int cc = 0; cc < VEC; ++cc) o[g][cc] = o[g][cc] * corr + pa * vA[cc];
+    }
+  }
+  // ---- merge the warps
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) { wm[warp * G + g] = m[g]; wl[warp * G + g] = l[g]; }
+#pragma unroll
+    for (int cc = 0; cc < VEC; ++cc) wo[((size_t)warp * G + g) * HD + head_elem<HD>(lane, cc)] = o[g][cc];
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < G * HD; i += kWaThreads) {
+    const int g = i / HD, e = i - g * HD;
+    float M = -INFINITY;
+    for (int w = 0; w < kWaWarps; ++w) M = fmaxf(M, wm[w * G + g]);
+    float L = 0.f, O = 0.f;
+    if (M > -INFINITY) {
+      for (int w = 0; w < kWaWarps; ++w) {
+        const float f = __expf(wm[w * G + g] - M);
+        L += wl[w * G + g] * f;
+        O += wo[((size_t)w * G + g) * HD + e] * f;
+      }
+    }
+    if (a.nsplit > 1) {
+      float* dst = a.part + ((((size_t)qi * dm.hkv + kvh) * a.nsplit + split) * G + g) * (HD + 2);
+      dst[e] = O;
+      if (e == 0) { dst[HD] = M; dst[HD + 1] = L; }
+    } else {
+      a.out[((size_t)qi * dm.hq + kvh * G + g) * HD + e] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+    }
+  }
+  if (*reinterpret_cast<volatile int*>(a.err) == (int)kDevBarrierTimeout) {
+    // a wait gave up: let the bulk copies still in flight land before the CTA retires
+    for (int i = 0; i < 2000; ++i) __nanosleep(100);
+    __syncthreads();
+  }
+}
+
+// Sum of the key splits' partial states: one CTA per (session, query head).
+__global__ void __launch_bounds__(128)
+wide_attn_combine_kernel(const float* __restrict__ part, int nsplit, int hq, int hkv, int hd, __nv_bfloat16* __restrict__ out) {
+  const int G = hq / hkv;
+  const int qi = blockIdx.x / hq, h = blockIdx.x % hq, kvh = h / G, g = h % G;
+  const float* base = part + (((size_t)qi * hkv + kvh) * nsplit * G + g) * (hd + 2);
+  const size_t stride = (size_t)G * (hd + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, base[s * stride + hd]);
+  float L = 0.f;
+  for (int s = 0; s < nsplit; ++s) L += M > -INFINITY ? base[s * stride + hd + 1] * __expf(base[s * stride + hd] - M) : 0.f;
+  for (int e = threadIdx.x; e < hd; e += 128) {
+    float O = 0.f;
+    for (int s = 0; s < nsplit; ++s)
+      if (M > -INFINITY) O += base[s * stride + e] * __expf(base[s * stride + hd] - M);
+    out[((size_t)qi * hq + h) * hd + e] = __float2bfloat16(L > 0.f ? O / L : 0.f);
   }
 }
 

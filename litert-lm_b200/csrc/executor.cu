@@ -299,11 +299,18 @@ static EncodeTiledFn encode_tiled_fn() {
 }
 
 // bf16 row-major [rows][cols]; box = 64 columns x 128 rows, 128-byte swizzle.
-CUtensorMap make_activation_map(const __nv_bfloat16* base, int rows, int cols) {
+ActMap make_activation_map(const __nv_bfloat16* base, int rows, int cols) {
+  ActMap m;
+  m.box128 = make_activation_map_box(base, rows, cols, kGemmBM);
+  m.box64 = make_activation_map_box(base, rows, cols, 64);
+  return m;
+}
+
+CUtensorMap make_activation_map_box(const __nv_bfloat16* base, int rows, int cols, int box_rows) {
   CUtensorMap tm;
   cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
-  cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)kGemmBM};
+  cuuint32_t box[2] = {(cuuint32_t)kGemmBK, (cuuint32_t)box_rows};
   cuuint32_t estr[2] = {1, 1};
   CUresult r = encode_tiled_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<__nv_bfloat16*>(base), dims,
                                  strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
@@ -348,7 +355,8 @@ static void launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t s
 // at most 8 splits) whose work units fill 90 % of the last round over the SMs,
 // else the divisor that fills it best.
 int pick_ksplit(int T, int n_tiles, int KB, int sms) {
-  const int tiles = n_tiles * ((T + kTsTok - 1) / kTsTok);
+  const int ntok = ts_tile_tokens(T);
+  const int tiles = n_tiles * ((T + ntok - 1) / ntok);
   int best = 1;
   double best_eff = 0.0;
   for (int s = 1; s <= 8; ++s) {
@@ -362,8 +370,9 @@ int pick_ksplit(int T, int n_tiles, int KB, int sms) {
   return best;
 }
 
-// Launches one int4 GEMM.  a_map must describe `A` ([rows >= T][K] bf16).
-void launch_gemm(cudaStream_t st, int mode, const CUtensorMap& a_map, const __nv_bfloat16* A,
+// Launches one int4 GEMM.  a_map must describe `A` ([rows >= T][K] bf16); a GEMM of at most 64 token rows
+// uses a_map64, the same tensor with a 64-row box.
+void launch_gemm(cudaStream_t st, int mode, const ActMap& a_map, const __nv_bfloat16* A,
                  const uint4* w4t, const float* s4t, const uint8_t* w4g, const float* s4g, int T, int N, int K,
                  int ksplit, bool geglu, float* outF, __nv_bfloat16* outB, int* err, int64_t* launches) {
   if (mode == B200LM_GEMM_TCGEN05) {
@@ -373,15 +382,23 @@ void launch_gemm(cudaStream_t st, int mode, const CUtensorMap& a_map, const __nv
     B2_CUDA(cudaGetDevice(&dev));
     B2_CHECK(dev >= 0 && dev < 64, kInternal, "device ordinal out of range");
     if (!sms_of[dev]) {
-      raise_dyn_smem(gemm_w4_ts_kernel<0>, (size_t)(kTsSmem));
-      raise_dyn_smem(gemm_w4_ts_kernel<1>, (size_t)(kTsSmem));
+      raise_dyn_smem(gemm_w4_ts_kernel<0, 256>, (size_t)ts_smem(256));
+      raise_dyn_smem(gemm_w4_ts_kernel<1, 256>, (size_t)ts_smem(256));
+      raise_dyn_smem(gemm_w4_ts_kernel<0, 128>, (size_t)ts_smem(128));
+      raise_dyn_smem(gemm_w4_ts_kernel<1, 128>, (size_t)ts_smem(128));
+      raise_dyn_smem(gemm_w4_ts_kernel<0, 64>, (size_t)ts_smem(64));
+      raise_dyn_smem(gemm_w4_ts_kernel<1, 64>, (size_t)ts_smem(64));
       B2_CUDA(cudaDeviceGetAttribute(&sms_of[dev], cudaDevAttrMultiProcessorCount, dev));
     }
     const int sms = sms_of[dev];
-    const int total = ((N + kTsRows - 1) / kTsRows) * ((T + kTsTok - 1) / kTsTok) * ksplit;
+    const int ntok = ts_tile_tokens(T);
+    const int total = ((N + kTsRows - 1) / kTsRows) * ((T + ntok - 1) / ntok) * ksplit;
     const int grid = total < sms ? total : sms;
-    if (geglu) launch_pdl(gemm_w4_ts_kernel<1>, dim3(grid), dim3(kTsThreads), kTsSmem, st, a_map, g);
-    else launch_pdl(gemm_w4_ts_kernel<0>, dim3(grid), dim3(kTsThreads), kTsSmem, st, a_map, g);
+#define B2_TS(EPI_, NTOK_, MAP_) launch_pdl(gemm_w4_ts_kernel<EPI_, NTOK_>, dim3(grid), dim3(ts_threads(NTOK_)), ts_smem(NTOK_), st, MAP_, g)
+    if (ntok == 64) { if (geglu) B2_TS(1, 64, a_map.box64); else B2_TS(0, 64, a_map.box64); }
+    else if (ntok == 128) { if (geglu) B2_TS(1, 128, a_map.box128); else B2_TS(0, 128, a_map.box128); }
+    else { if (geglu) B2_TS(1, 256, a_map.box128); else B2_TS(0, 256, a_map.box128); }
+#undef B2_TS
   } else {
     B2_CHECK(ksplit == 1, kInternal, "the check GEMM does not split K");
     dim3 grid(geglu ? N / 32 : N / 16, (T + 7) / 8);
@@ -417,6 +434,8 @@ void* Executor::alloc(size_t bytes, bool zero) {
   if (zero) B2_CUDA(cudaMemset(p, 0, std::max<size_t>(bytes, 256)));
   return p;
 }
+
+static void launch_wide_attn(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a);
 
 std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B200LmConfig& cfg) {
   auto e = std::unique_ptr<Executor>(new Executor());
@@ -562,6 +581,9 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   if (e->decode_mode == B200LM_DECODE_WIDE) {
     int* ws = reinterpret_cast<int*>(e->alloc(sizeof(int) * 3 * kWideMax, true));
     e->wide = WideState{ws, ws + kWideMax, ws + 2 * kWideMax};
+    launch_wide_attn(e->stream, d, 0, e->smem_optin, WideAttnArgs{});
+    e->wide_part = reinterpret_cast<float*>(
+        e->alloc(sizeof(float) * (size_t)e->n_sessions * d.hkv * kWideMaxSplits * d.group() * (d.hd + 2), true));
   }
   a.advance = 1;
   // the one-kernel-per-phase fallback drives one session; the persistent kernels carry all of them
@@ -1031,11 +1053,53 @@ void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
   launches += (int64_t)nsteps * (5 * d.n_layers + 2);
 }
 
+// The streaming attention of a wide step, instantiated for the cache type, head size and group size.
+template <typename T, int HD, int G>
+static void launch_wide_attn_t(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, WideAttnArgs a) {
+  const size_t fixed = wa_fixed_bytes(HD, G);
+  const int stage = wa_stage_bytes<T, HD>();
+  const int stages = (int)std::min<size_t>(kWaMaxStages, (smem_optin - 1024 - fixed) / stage);
+  B2_CHECK(stages >= 2, kUnimplemented, "the wide decode attention does not fit the device's shared memory");
+  a.stages = stages;
+  const size_t smem = fixed + (size_t)stages * stage;
+  raise_dyn_smem(wide_attn_kernel<T, HD, G>, smem);
+  if (nb <= 0) return;                             // set-up only (executor creation, outside any stream capture)
+  wide_attn_kernel<T, HD, G><<<nb * d.hkv * a.nsplit, kWaThreads, smem, st>>>(d, a);
+}
+template <typename T, int HD>
+static void launch_wide_attn_g(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
+  switch (d.group()) {
+    case 1: launch_wide_attn_t<T, HD, 1>(st, d, nb, smem_optin, a); break;
+    case 2: launch_wide_attn_t<T, HD, 2>(st, d, nb, smem_optin, a); break;
+    case 4: launch_wide_attn_t<T, HD, 4>(st, d, nb, smem_optin, a); break;
+    default: throw Error{kUnimplemented, "query heads per kv head must be 1, 2 or 4"};
+  }
+}
+template <typename T>
+static void launch_wide_attn_h(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
+  switch (d.hd) {
+    case 32: launch_wide_attn_g<T, 32>(st, d, nb, smem_optin, a); break;
+    case 64: launch_wide_attn_g<T, 64>(st, d, nb, smem_optin, a); break;
+    case 128: launch_wide_attn_g<T, 128>(st, d, nb, smem_optin, a); break;
+    case 256: launch_wide_attn_g<T, 256>(st, d, nb, smem_optin, a); break;
+    default: throw Error{kUnimplemented, "head size must be 32, 64, 128 or 256"};
+  }
+}
+static void launch_wide_attn(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
+  if (d.kv_dtype == 0) launch_wide_attn_h<float>(st, d, nb, smem_optin, a);
+  else launch_wide_attn_h<__nv_bfloat16>(st, d, nb, smem_optin, a);
+}
+
 // One wide step for sessions [first, first + nb): the token rows of the GEMMs are the sessions.
 void Executor::wide_step(int nb, int first) {
   const ModelDims& d = model->dims;
   int* err = &dargs.st->err;
   const int mode = B200LM_GEMM_TCGEN05;
+  // key splits so that few sessions still fill the SMs: one CTA per (session, kv head, split)
+  const int nsplit = std::max(1, std::min(kWideMaxSplits, n_sms / std::max(1, nb * d.hkv)));
+  // The streaming kernel keeps one CTA per SM busy with deep bulk-copy rings; with well over one (session, kv head)
+  // pair per SM the plain-load kernel, several CTAs resident per SM, overlaps more and has no second wave.
+  const bool stream_attn = nb * d.hkv * 2 <= n_sms * 3;
   const size_t attn_smem = sizeof(float) * ((size_t)(d.group() + 2) * d.hd + (size_t)8 * d.group() * (d.hd + 2));
   pf_embed_norm_kernel<<<nb, kPfThreads, sizeof(float) * d.d, stream>>>(wide.tok, model->embed_rows, model->embed_scale,
                                                                         model->layers_host[0].g_pre_attn, d.d, d.vocab, d.eps,
@@ -1055,25 +1119,36 @@ void Executor::wide_step(int nb, int first) {
       wide_sum_parts_kernel<<<(unsigned)((count / 4 + 255) / 256), 256, 0, stream>>>(pf_parts, ks_q, count, count, pf_qkv);
       ++*nl;
     }
-    AttnJob j;
-    memset(&j, 0, sizeof j);
-    j.qkv = pf_qkv;
-    j.pos = wide.pos;
-    j.page_table = page_table_dev + (size_t)first * pages_per_seq;
-    j.pages_per_seq = pages_per_seq;
-    j.seq_stride = 1;
-    j.is_global = L.is_global;
-    j.nsplit = 1;
-    j.appended = 0;                                 // the kernel norms, rotates and appends this step's K / V rows
-    j.g_q = L.g_q;
-    j.g_k = L.g_k;
-    j.cosT = model->rope_cos[L.is_global];
-    j.sinT = model->rope_sin[L.is_global];
-    j.kv = kv_host[li];
-    j.out_bf16 = pf_attn;
-    j.err = err;
-    pf_attn_kernel<<<nb * d.hkv, 256, attn_smem, stream>>>(d, j);
+    if (stream_attn) {
+    WideAttnArgs wa{pf_qkv, wide.pos, page_table_dev + (size_t)first * pages_per_seq, pages_per_seq, L.is_global, nsplit, 0,
+                    L.g_q, L.g_k, model->rope_cos[L.is_global], model->rope_sin[L.is_global], kv_host[li], wide_part, pf_attn, err};
+    launch_wide_attn(stream, d, nb, smem_optin, wa);
     ++*nl;
+    if (nsplit > 1) {
+      wide_attn_combine_kernel<<<nb * d.hq, 128, 0, stream>>>(wide_part, nsplit, d.hq, d.hkv, d.hd, pf_attn);
+      ++*nl;
+    }
+    } else {
+      AttnJob j;
+      memset(&j, 0, sizeof j);
+      j.qkv = pf_qkv;
+      j.pos = wide.pos;
+      j.page_table = page_table_dev + (size_t)first * pages_per_seq;
+      j.pages_per_seq = pages_per_seq;
+      j.seq_stride = 1;
+      j.is_global = L.is_global;
+      j.nsplit = 1;
+      j.appended = 0;                               // the kernel norms, rotates and appends this step's K / V rows
+      j.g_q = L.g_q;
+      j.g_k = L.g_k;
+      j.cosT = model->rope_cos[L.is_global];
+      j.sinT = model->rope_sin[L.is_global];
+      j.kv = kv_host[li];
+      j.out_bf16 = pf_attn;
+      j.err = err;
+      pf_attn_kernel<<<nb * d.hkv, 256, attn_smem, stream>>>(d, j);
+      ++*nl;
+    }
     const int ks_o = pick_ksplit(nb, (d.d + kTsRows - 1) / kTsRows, d.nq() / 64, n_sms);
     launch_gemm(stream, mode, tm_attn, pf_attn, L.wo, L.so, Gm.wo, Gm.so, nb, d.d, d.nq(), ks_o, false, pf_parts, nullptr, err, nl);
     launch_resid_norm(stream, pf_parts, ks_o, nb, d, L.g_post_attn, L.g_pre_ffn, pf_xres, pf_h);

@@ -264,7 +264,7 @@ static void run_gemm_common(int device, int mode, const uint8_t* packed_rows, co
   B2_CUDA(cudaMemcpy(dsg.p, sg.data(), sg.size() * 4, cudaMemcpyHostToDevice));
   const int64_t out_cols = geglu ? ffn : n;
   DevBuf of((size_t)std::max(ksplit, 1) * t * n * 4, true), ob((size_t)t * out_cols * 2, true);
-  CUtensorMap tm{};
+  ActMap tm{};
   if (mode == B200LM_GEMM_TCGEN05) tm = make_activation_map(a16.as<__nv_bfloat16>(), tp, (int)k);
   cudaEvent_t e0, e1;
   B2_CUDA(cudaEventCreate(&e0));

@@ -22,8 +22,8 @@
 // Warp roles: 0 = TMA producer, 1 = TMEM owner + MMA issue, 2..5 = int4
 // expansion, 6..21 = epilogue.
 //
-// TMEM columns: [0,256) accumulator, then kTsStages slots of 32 columns
-// holding one expanded 128 x 64 weight tile each.
+// TMEM columns: [0, NTOK) accumulator, then one slot of 32 columns per pipeline
+// stage holding one expanded 128 x 64 weight tile each.
 #pragma once
 #include "prefill_ops.cuh"
 
@@ -33,13 +33,23 @@ constexpr int kTsStages = 5;
 constexpr int kTsRows = 128;                        // weight rows per tile
 constexpr int kTsTok = 256;                         // tokens per tile
 constexpr int kTsAcols = 32;                        // TMEM columns of one expanded 128 x 64 weight tile
-constexpr int kTsDeqWarps = 4, kTsEpiWarps = 16;
-constexpr int kTsThreads = 64 + 32 * (kTsDeqWarps + kTsEpiWarps);
+// Warps per role and token width: narrow tiles give the warps their smaller epilogue does not need to the
+// int4 expansion (two warps per 32 accumulator lanes, half a weight row each).  The epilogue needs one warp
+// per 32 lanes x 64 token columns.
+__host__ __device__ constexpr int ts_deq_warps(int ntok) { return ntok >= 256 ? 4 : 8; }
+__host__ __device__ constexpr int ts_epi_warps(int ntok) { return 4 * (ntok / 64); }
+__host__ __device__ constexpr int ts_threads(int ntok) { return 64 + 32 * (ts_deq_warps(ntok) + ts_epi_warps(ntok)); }
 constexpr int kTsStageX = kTsTok * kGemmBK * 2;     // activation tile, 32 KB
-constexpr int kTsStageBytes = kTsStageX + kGemmStageQ;
-constexpr int kTsSmem = kTsStages * kTsStageBytes + 1024 + 512;
 constexpr int kTsTmemCols = 512;
-static_assert(kTsTok + kTsStages * kTsAcols <= kTsTmemCols, "TMEM budget");
+// Pipeline depth per token width.  A stage holds one k block: NTOK x 64 activations and 4 KB of int4 weights.
+// The weights come from HBM, so what bounds a narrow tile is the bytes in flight per SM (stages x 4 KB over a
+// round trip of a few microseconds), not the MMA: narrow tiles spend the shared memory and the tensor-memory
+// columns the accumulator leaves on more stages.
+__host__ __device__ constexpr int ts_stages(int ntok) { return ntok >= 256 ? kTsStages : ntok == 128 ? 8 : 12; }
+__host__ __device__ constexpr int ts_smem(int ntok) { return ts_stages(ntok) * (ntok * kGemmBK * 2 + kGemmStageQ) + 1024 + 512; }
+static_assert(256 + ts_stages(256) * kTsAcols <= kTsTmemCols && 128 + ts_stages(128) * kTsAcols <= kTsTmemCols &&
+                  64 + ts_stages(64) * kTsAcols <= kTsTmemCols, "TMEM budget");
+static_assert(ts_smem(256) <= 227 * 1024 && ts_smem(128) <= 227 * 1024 && ts_smem(64) <= 227 * 1024, "shared memory budget");
 
 // A operand in tensor memory, B through a shared-memory descriptor
 __device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc,
@@ -84,14 +94,21 @@ __device__ __forceinline__ TsTile ts_tile(int tile, int n_tiles, int t_tiles) {
 
 // EPI 0: fp32 partials outF[ks][T][N].  EPI 1: GeGLU; tile rows alternate
 // gate (even) and up (odd) rows of one ffn feature, output bf16 outB[T][N/2].
-template <int EPI>
-__global__ void __launch_bounds__(kTsThreads, 1)
+//
+// NTOK is the token width of a tile (the N of the MMA): 256 for prefill; 128 or 64 when the whole GEMM has
+// no more token rows than that (the wide decode step, short prompts), which cuts the activation bytes every
+// CTA re-reads per k block and the MMA time in proportion.  tmX must have a box of min(NTOK, 128) rows.
+template <int EPI, int NTOK>
+__global__ void __launch_bounds__(ts_threads(NTOK), 1)
 gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
-  constexpr int S = kTsStages;
+  constexpr int kTsDeqWarps = ts_deq_warps(NTOK), kTsEpiWarps = ts_epi_warps(NTOK);
+  constexpr int S = ts_stages(NTOK);
+  constexpr int kStageX = NTOK * kGemmBK * 2;       // activation tile of one stage
+  constexpr uint32_t kStageTx = NTOK * kGemmBK * 2 + kGemmStageQ;
   extern __shared__ unsigned char gsm_raw[];
   unsigned char* gsm = reinterpret_cast<unsigned char*>(((uintptr_t)gsm_raw + 1023) & ~(uintptr_t)1023);
   unsigned char* sX = gsm;
-  unsigned char* sQ = gsm + S * kTsStageX;
+  unsigned char* sQ = gsm + S * kStageX;
   uint64_t* bars = reinterpret_cast<uint64_t*>(sQ + S * kGemmStageQ);
   uint64_t* full_bar = bars;              // [S] TMA bytes landed
   uint64_t* deq_bar = bars + S;           // [S] expanded weights are in TMEM
@@ -104,7 +121,7 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
   const int KB = g.K / kGemmBK;
   const int nkb = KB / g.ksplit;
   const int n_tiles = (g.N + kTsRows - 1) / kTsRows;
-  const int t_tiles = (g.T + kTsTok - 1) / kTsTok;
+  const int t_tiles = (g.T + NTOK - 1) / NTOK;
   const int total = n_tiles * t_tiles * g.ksplit;
   const int my_tiles = (int)blockIdx.x < total ? (total - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
 
@@ -123,7 +140,7 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_w = tmem_base + kTsTok;
+  const uint32_t tmem_w = tmem_base + NTOK;         // weight slots follow the accumulator columns
   // barriers and TMEM are set up: from here on the kernel reads what its predecessor wrote
   pdl_wait();
   pdl_launch_dependents();
@@ -139,11 +156,11 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
         const int s = it % S, n = it / S;
         if (n > 0) ok = mbar_wait(&empty_bar[s], (n - 1) & 1, g.err);
         if (ok && lane == 0) {
-          mbar_arrive_expect_tx(&full_bar[s], kTsStageBytes);
+          mbar_arrive_expect_tx(&full_bar[s], kStageTx);
 #pragma unroll
-          for (int h = 0; h < kTsTok / 128; ++h)
-            tma_load_2d(sX + s * kTsStageX + h * 128 * 128, &tmX, (tl.ks * nkb + kb) * kGemmBK,
-                        tl.t_tile * kTsTok + h * 128, &full_bar[s]);
+          for (int h = 0; h < (NTOK + 127) / 128; ++h)
+            tma_load_2d(sX + s * kStageX + h * 128 * 128, &tmX, (tl.ks * nkb + kb) * kGemmBK,
+                        tl.t_tile * NTOK + h * 128, &full_bar[s]);
           bulk_load_1d(sQ + s * kGemmStageQ, wtile + (size_t)kb * kGemmStageQ, kGemmStageQ, &full_bar[s]);
         }
         __syncwarp();
@@ -151,7 +168,7 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
     }
   } else if (warp == 1) {
     // ---- MMA issue
-    const uint32_t idesc = umma_idesc_bf16(kTsRows, kTsTok);
+    const uint32_t idesc = umma_idesc_bf16(kTsRows, NTOK);
     int it = 0;
     bool ok = true;
     for (int li = 0; li < my_tiles && ok; ++li) {
@@ -163,7 +180,7 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
         if (!ok) break;
         tc_fence_after();
         if (lane == 0) {
-          const uint64_t xd = umma_desc_sw128(smem_u32(sX + s * kTsStageX));
+          const uint64_t xd = umma_desc_sw128(smem_u32(sX + s * kStageX));
 #pragma unroll
           for (int k = 0; k < kGemmBK / 16; ++k)   // 16 bf16 along K per MMA: 8 TMEM columns, 32 bytes of X
             umma_bf16_ts(tmem_base, tmem_w + s * kTsAcols + k * 8, xd + (uint64_t)(k * 2), idesc, (kb | k) ? 1u : 0u);
@@ -175,8 +192,11 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
       __syncwarp();
     }
   } else if (warp < 2 + kTsDeqWarps) {
-    // ---- int4 -> bf16 expansion into TMEM: this thread does the 64 k (32 columns) of its weight row
+    // ---- int4 -> bf16 expansion into TMEM: this thread does the 64 k (32 columns) of its weight row, or one
+    // half of them when two warps share the 32 lanes
     const int quarter = warp & 3;                  // TMEM lanes 32*quarter .. +31 belong to this warp
+    constexpr int kHalves = 8 / kTsDeqWarps;       // halves of a row per thread: 2 with four warps, 1 with eight
+    const int half0 = kTsDeqWarps == 8 ? (warp - 2) >> 2 : 0;
     const int row = quarter * 32 + lane;
     const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
     const int iters = my_tiles * nkb;
@@ -189,7 +209,8 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
       if (!ok) break;
       tc_fence_after();
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
+      for (int hh = 0; hh < kHalves; ++hh) {
+        const int half = half0 + hh;
         const uint4 q = *reinterpret_cast<const uint4*>(sQ + s * kGemmStageQ + row * 32 + half * 16);
         const uint32_t qw[4] = {q.x, q.y, q.z, q.w};
         uint32_t r[16];
@@ -222,14 +243,17 @@ gemm_w4_ts_kernel(const __grid_constant__ CUtensorMap tmX, GemmArgs g) {
       if (!ok) break;
       tc_fence_after();
       const int c0 = second * 64;
-      const int t0 = tl.t_tile * kTsTok + c0;
+      const int t0 = tl.t_tile * NTOK + c0;
       uint32_t v0[32], v1[32];
-      tmem_ld32(tmem_base + lane_base + c0, v0);
-      tmem_ld32(tmem_base + lane_base + c0 + 32, v1);
+      if (c0 < NTOK) {
+        tmem_ld32(tmem_base + lane_base + c0, v0);
+        tmem_ld32(tmem_base + lane_base + c0 + 32, v1);
+      }
       // the accumulator is in registers: hand it back before the stores
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty);
+      if (c0 >= NTOK) continue;                      // a narrow tile has no columns for this warp
       const float sc = g.wscale[tl.n_tile * kTsRows + row];
       if constexpr (EPI == 0) {
         const int nrow = tl.n_tile * kTsRows + row;

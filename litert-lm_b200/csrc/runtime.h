@@ -56,9 +56,18 @@ struct Model {
   static std::shared_ptr<Model> load(const uint8_t* image, size_t n, int device, bool want_tc);
 };
 
-CUtensorMap make_activation_map(const __nv_bfloat16* base, int rows, int cols);
-int pick_ksplit(int tiles, int KB, int sms);
-void launch_gemm(cudaStream_t st, int mode, const CUtensorMap& a_map, const __nv_bfloat16* A, const uint4* w4t,
+// An activation matrix [rows][cols] bf16 as the GEMM's token operand: the same tensor with a 128-row and a
+// 64-row copy box (the kernel's token tile is 256 / 128 or 64 wide).
+struct ActMap {
+  CUtensorMap box128;
+  CUtensorMap box64;
+};
+// token width of the GEMM tile for T token rows
+inline int ts_tile_tokens(int T) { return T <= 64 ? 64 : T <= 128 ? 128 : 256; }
+CUtensorMap make_activation_map_box(const __nv_bfloat16* base, int rows, int cols, int box_rows);
+ActMap make_activation_map(const __nv_bfloat16* base, int rows, int cols);
+int pick_ksplit(int T, int n_tiles, int KB, int sms);
+void launch_gemm(cudaStream_t st, int mode, const ActMap& a_map, const __nv_bfloat16* A, const uint4* w4t,
                  const float* s4t, const uint8_t* w4g, const float* s4g, int T, int N, int K, int ksplit, bool geglu,
                  float* outF, __nv_bfloat16* outB, int* err, int64_t* launches);
 
@@ -137,6 +146,7 @@ class Executor {
   cudaGraphExec_t graph_exec = nullptr;
   // wide lockstep decode (B200LM_DECODE_WIDE)
   WideState wide{nullptr, nullptr, nullptr};
+  float* wide_part = nullptr;       // key-split partial states of the wide attention
   int* pin_wide = nullptr;          // staging of the wide state words
   std::map<std::pair<int, int>, cudaGraphExec_t> wide_graphs;   // one step, keyed by (sessions, first session)
   int64_t wide_per_step = 0;        // kernel launches of one wide step
@@ -151,7 +161,7 @@ class Executor {
   __nv_bfloat16* pf_attn = nullptr;
   __nv_bfloat16* pf_act = nullptr;
   float* pf_parts = nullptr;
-  CUtensorMap tm_h{}, tm_attn{}, tm_act{};
+  ActMap tm_h{}, tm_attn{}, tm_act{};
   bool attn_tc = false;             // tensor-core prefill attention in use
   __nv_bfloat16* pf_q = nullptr;    // [t_pad][hq][hd] normalised, rotated, scaled queries
   CUtensorMap tm_q{};

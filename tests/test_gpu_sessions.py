@@ -76,7 +76,7 @@ def test_single_session_calls_leave_the_other_sessions_alone(pkg, orc, models):
 def test_session_count_is_checked(pkg, models):
     cfg, rec, img = models("tiny")
     with pytest.raises(pkg.StatusError) as e:
-        pkg.B200LlmExecutor(img, n_sessions=5)
+        pkg.B200LlmExecutor(img, n_sessions=129)
     assert e.value.code == pkg.INVALID_ARGUMENT
     ex = pkg.B200LlmExecutor(img, n_sessions=2)
     with pytest.raises(pkg.StatusError):
