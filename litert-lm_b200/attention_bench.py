@@ -48,6 +48,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="two prefill and two decode shapes only")
     ap.add_argument("--repeat", type=int, default=20)
+    ap.add_argument("--register-kernel", action="store_true", help="decode: the register-resident split kernel instead of the streaming one")
     args = ap.parse_args()
     graft.build()
     pkg = graft.load_package()
@@ -68,16 +69,19 @@ def main() -> None:
                               "roofline": {"bound": "tensor", "achieved": tf, "peak": tensor, "unit": "TFLOP/s",
                                            "frac": tf / tensor, "of": src}}), flush=True)
     shapes = ((1024, 1), (32768, 64)) if args.quick else tuple((s, b) for s in (1024, 4096, 16384, 32768)
-                                                              for b in (1, 8, 64))
+                                                              for b in (1, 4, 16, 64))
     for s, batch in shapes:
         k = rng.standard_normal((s, HKV, HD), dtype=np.float32)
         v = rng.standard_normal((s, HKV, HD), dtype=np.float32)
         q = rng.standard_normal((batch, HQ, HD), dtype=np.float32)
-        nsplit = max(2, min(64, s // 256))
-        _, ms = pkg.ops.attention(q, k, v, nsplit=nsplit, repeat=args.repeat, kv_bf16=True, private_caches=True)
+        # about two (sequence, kv head, split) work items per SM, splits of at least 256 keys
+        nsplit = max(2, min(64, s // 256, -(-2 * 148 // (batch * HKV))))
+        _, ms = pkg.ops.attention(q, k, v, nsplit=nsplit, repeat=args.repeat, kv_bf16=True, private_caches=True,
+                                  register_kernel=args.register_kernel)
         nbytes = 2.0 * s * HKV * HD * 2 * batch
         gbs = nbytes / (ms * 1e-3) / 1e9
-        print(json.dumps({"op": "decode_attention", "kernel": "attn_decode_kernel + attn_combine_kernel", "kv_len": s,
+        print(json.dumps({"op": "decode_attention", "kernel": ("attn_decode_kernel + attn_combine_kernel" if args.register_kernel else
+                                                            "wide_attn_kernel + wide_attn_combine_kernel"), "kv_len": s,
                           "batch": batch, "nsplit": nsplit, "page": 256, "kv_dtype": "bf16", "ms": ms, "bytes": nbytes,
                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s",
                                        "frac": gbs / hbm, "of": src,

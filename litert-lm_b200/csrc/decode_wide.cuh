@@ -7,6 +7,7 @@
 // This file holds the two small kernels the step adds to the prefill kernels; the step itself is
 // Executor::launch_wide_steps.
 #pragma once
+#include <algorithm>
 #include "decode_ops.cuh"
 #include "prefill_ops.cuh"
 
@@ -94,6 +95,9 @@ struct WideAttnArgs {
   float* part;               // nsplit > 1: [session][kv head][split][G][hd + 2] (o, then m and l)
   __nv_bfloat16* out;        // nsplit == 1: [session][hq * hd]
   int* err;
+  int seq_stride;            // 1: session i has row i of the page table; 0: every query reads sequence 0
+  int appended;              // 1: q rows are final (no norm, no rotation) and every K / V row is already in the cache
+  float* out_f32;            // nsplit == 1: the same output in fp32 (operator-level callers), optional
 };
 
 template <typename T, int HD>
@@ -128,7 +132,7 @@ wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
     if (threadIdx.x == 0) atomicExch(a.err, (int)kDevBadPosition);
     pos = 0;
   }
-  const int* ptab = a.page_table + (size_t)qi * a.pages_per_seq;
+  const int* ptab = a.page_table + (size_t)(a.seq_stride ? qi : 0) * a.pages_per_seq;
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], kWaWarps); }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -139,7 +143,7 @@ wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
   // requested before the prologue below (they depend on the position only), so their latency hides behind it.
   int k0, k1;
   attn_split_range(dm, pos, a.is_global, a.nsplit, split, &k0, &k1);
-  const bool has_cur = k1 == pos + 1 && k1 > k0;
+  const bool has_cur = !a.appended && k1 == pos + 1 && k1 > k0;
   const int k1s = has_cur ? pos : k1;                  // streamed keys: [k0, k1s)
   const int cb0 = k0 / kWaChunk;
   const int nchunks = k1s > k0 ? (k1s + kWaChunk - 1) / kWaChunk - cb0 : 0;
@@ -156,8 +160,11 @@ wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
   // ---- this step's q heads (normed, rotated, scaled), k head and v head
   const float* row = a.qkv + (size_t)qi * dm.nqkv();
   const float att_scale = rsqrtf((float)HD);
-  for (int h = warp; h < G + 2; h += kWaWarps) {
-    if (h <= G) {
+  for (int h = warp; h < (a.appended ? G : G + 2); h += kWaWarps) {
+    if (a.appended) {                                  // final q rows: only the attention scale
+      const float* src = row + (size_t)(kvh * G + h) * HD;
+      for (int e = lane; e < HD; e += 32) q_s[h * HD + e] = src[e] * att_scale;
+    } else if (h <= G) {
       const float* src = h < G ? row + (size_t)(kvh * G + h) * HD : row + dm.nq() + (size_t)kvh * HD;
       const float* gain = h < G ? a.g_q : a.g_k;
       float* dst = h < G ? q_s + h * HD : k_s;
@@ -178,7 +185,7 @@ wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
     }
   }
   __syncthreads();
-  if (split == 0) {          // append: exactly one CTA per (session, kv head)
+  if (split == 0 && !a.appended) {          // append: exactly one CTA per (session, kv head)
     const int page = ptab[pos / kPage], slot = pos % kPage;
     const size_t off = (((size_t)page * dm.hkv + kvh) * kPage + slot) * HD;
     T* kw = reinterpret_cast<T*>(a.kv.k);
@@ -298,7 +305,10 @@ wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
       dst[e] = O;
       if (e == 0) { dst[HD] = M; dst[HD + 1] = L; }
     } else {
-      a.out[((size_t)qi * dm.hq + kvh * G + g) * HD + e] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+      const float val = L > 0.f ? O / L : 0.f;
+      const size_t oi = ((size_t)qi * dm.hq + kvh * G + g) * HD + e;
+      if (a.out) a.out[oi] = __float2bfloat16(val);
+      if (a.out_f32) a.out_f32[oi] = val;
     }
   }
   if (*reinterpret_cast<volatile int*>(a.err) == (int)kDevBarrierTimeout) {
@@ -310,7 +320,8 @@ wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
 
 // Sum of the key splits' partial states: one CTA per (session, query head).
 __global__ void __launch_bounds__(128)
-wide_attn_combine_kernel(const float* __restrict__ part, int nsplit, int hq, int hkv, int hd, __nv_bfloat16* __restrict__ out) {
+wide_attn_combine_kernel(const float* __restrict__ part, int nsplit, int hq, int hkv, int hd, __nv_bfloat16* __restrict__ out,
+                         float* __restrict__ out_f32) {
   const int G = hq / hkv;
   const int qi = blockIdx.x / hq, h = blockIdx.x % hq, kvh = h / G, g = h % G;
   const float* base = part + (((size_t)qi * hkv + kvh) * nsplit * G + g) * (hd + 2);
@@ -323,8 +334,48 @@ wide_attn_combine_kernel(const float* __restrict__ part, int nsplit, int hq, int
     float O = 0.f;
     for (int s = 0; s < nsplit; ++s)
       if (M > -INFINITY) O += base[s * stride + e] * __expf(base[s * stride + hd] - M);
-    out[((size_t)qi * hq + h) * hd + e] = __float2bfloat16(L > 0.f ? O / L : 0.f);
+    const float val = L > 0.f ? O / L : 0.f;
+    if (out) out[((size_t)qi * hq + h) * hd + e] = __float2bfloat16(val);
+    if (out_f32) out_f32[((size_t)qi * hq + h) * hd + e] = val;
   }
+}
+
+// Host side: the kernel instantiated for the cache type, head size and group size.  nb <= 0 only sets the
+// kernel's shared-memory attribute (executor creation, outside any stream capture).
+template <typename T, int HD, int G>
+inline void launch_wide_attn_t(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, WideAttnArgs a) {
+  const size_t fixed = wa_fixed_bytes(HD, G);
+  const int stage = wa_stage_bytes<T, HD>();
+  const int stages = (int)std::min<size_t>(kWaMaxStages, (smem_optin - 1024 - fixed) / stage);
+  B2_CHECK(stages >= 2, kUnimplemented, "the streaming decode attention does not fit the device's shared memory");
+  a.stages = stages;
+  const size_t smem = fixed + (size_t)stages * stage;
+  raise_dyn_smem(wide_attn_kernel<T, HD, G>, smem);
+  if (nb <= 0) return;
+  wide_attn_kernel<T, HD, G><<<nb * d.hkv * a.nsplit, kWaThreads, smem, st>>>(d, a);
+}
+template <typename T, int HD>
+inline void launch_wide_attn_g(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
+  switch (d.group()) {
+    case 1: launch_wide_attn_t<T, HD, 1>(st, d, nb, smem_optin, a); break;
+    case 2: launch_wide_attn_t<T, HD, 2>(st, d, nb, smem_optin, a); break;
+    case 4: launch_wide_attn_t<T, HD, 4>(st, d, nb, smem_optin, a); break;
+    default: throw Error{kUnimplemented, "query heads per kv head must be 1, 2 or 4"};
+  }
+}
+template <typename T>
+inline void launch_wide_attn_h(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
+  switch (d.hd) {
+    case 32: launch_wide_attn_g<T, 32>(st, d, nb, smem_optin, a); break;
+    case 64: launch_wide_attn_g<T, 64>(st, d, nb, smem_optin, a); break;
+    case 128: launch_wide_attn_g<T, 128>(st, d, nb, smem_optin, a); break;
+    case 256: launch_wide_attn_g<T, 256>(st, d, nb, smem_optin, a); break;
+    default: throw Error{kUnimplemented, "head size must be 32, 64, 128 or 256"};
+  }
+}
+inline void launch_wide_attn(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
+  if (d.kv_dtype == 0) launch_wide_attn_h<float>(st, d, nb, smem_optin, a);
+  else launch_wide_attn_h<__nv_bfloat16>(st, d, nb, smem_optin, a);
 }
 
 // out[t][:] = sum of the split-K partials parts[p][t][:], rows of `cols` floats.

@@ -435,8 +435,6 @@ void* Executor::alloc(size_t bytes, bool zero) {
   return p;
 }
 
-static void launch_wide_attn(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a);
-
 std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B200LmConfig& cfg) {
   auto e = std::unique_ptr<Executor>(new Executor());
   e->model = model;
@@ -1053,43 +1051,6 @@ void Executor::launch_decode_steps(int nsteps, int ncols, int first_session) {
   launches += (int64_t)nsteps * (5 * d.n_layers + 2);
 }
 
-// The streaming attention of a wide step, instantiated for the cache type, head size and group size.
-template <typename T, int HD, int G>
-static void launch_wide_attn_t(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, WideAttnArgs a) {
-  const size_t fixed = wa_fixed_bytes(HD, G);
-  const int stage = wa_stage_bytes<T, HD>();
-  const int stages = (int)std::min<size_t>(kWaMaxStages, (smem_optin - 1024 - fixed) / stage);
-  B2_CHECK(stages >= 2, kUnimplemented, "the wide decode attention does not fit the device's shared memory");
-  a.stages = stages;
-  const size_t smem = fixed + (size_t)stages * stage;
-  raise_dyn_smem(wide_attn_kernel<T, HD, G>, smem);
-  if (nb <= 0) return;                             // set-up only (executor creation, outside any stream capture)
-  wide_attn_kernel<T, HD, G><<<nb * d.hkv * a.nsplit, kWaThreads, smem, st>>>(d, a);
-}
-template <typename T, int HD>
-static void launch_wide_attn_g(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
-  switch (d.group()) {
-    case 1: launch_wide_attn_t<T, HD, 1>(st, d, nb, smem_optin, a); break;
-    case 2: launch_wide_attn_t<T, HD, 2>(st, d, nb, smem_optin, a); break;
-    case 4: launch_wide_attn_t<T, HD, 4>(st, d, nb, smem_optin, a); break;
-    default: throw Error{kUnimplemented, "query heads per kv head must be 1, 2 or 4"};
-  }
-}
-template <typename T>
-static void launch_wide_attn_h(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
-  switch (d.hd) {
-    case 32: launch_wide_attn_g<T, 32>(st, d, nb, smem_optin, a); break;
-    case 64: launch_wide_attn_g<T, 64>(st, d, nb, smem_optin, a); break;
-    case 128: launch_wide_attn_g<T, 128>(st, d, nb, smem_optin, a); break;
-    case 256: launch_wide_attn_g<T, 256>(st, d, nb, smem_optin, a); break;
-    default: throw Error{kUnimplemented, "head size must be 32, 64, 128 or 256"};
-  }
-}
-static void launch_wide_attn(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, const WideAttnArgs& a) {
-  if (d.kv_dtype == 0) launch_wide_attn_h<float>(st, d, nb, smem_optin, a);
-  else launch_wide_attn_h<__nv_bfloat16>(st, d, nb, smem_optin, a);
-}
-
 // One wide step for sessions [first, first + nb): the token rows of the GEMMs are the sessions.
 void Executor::wide_step(int nb, int first) {
   const ModelDims& d = model->dims;
@@ -1121,11 +1082,12 @@ void Executor::wide_step(int nb, int first) {
     }
     if (stream_attn) {
     WideAttnArgs wa{pf_qkv, wide.pos, page_table_dev + (size_t)first * pages_per_seq, pages_per_seq, L.is_global, nsplit, 0,
-                    L.g_q, L.g_k, model->rope_cos[L.is_global], model->rope_sin[L.is_global], kv_host[li], wide_part, pf_attn, err};
+                    L.g_q, L.g_k, model->rope_cos[L.is_global], model->rope_sin[L.is_global], kv_host[li], wide_part, pf_attn, err,
+                    1, 0, nullptr};
     launch_wide_attn(stream, d, nb, smem_optin, wa);
     ++*nl;
     if (nsplit > 1) {
-      wide_attn_combine_kernel<<<nb * d.hq, 128, 0, stream>>>(wide_part, nsplit, d.hq, d.hkv, d.hd, pf_attn);
+      wide_attn_combine_kernel<<<nb * d.hq, 128, 0, stream>>>(wide_part, nsplit, d.hq, d.hkv, d.hd, pf_attn, nullptr);
       ++*nl;
     }
     } else {

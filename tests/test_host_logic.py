@@ -151,3 +151,33 @@ def test_algorithmic_work_formulas(mio):
     assert cfg.vocab * cfg.d_model // 2 == 150_994_944
     assert cfg.decode_bytes_per_token() == 536_848_896
     assert abs(cfg.prefill_flops(1024) - 1.473e12) / 1.473e12 < 2e-3
+
+
+def test_xnnpack_timing_baseline_tracks_the_oracle(orc, models):
+    """The XNNPACK leg of the CPU arm (int8 activations) is a timing baseline, not a parity reference, but it must
+    compute the same model: same arg-max and a high cosine on a small case.  Skipped where torch's XNNPACK symbols
+    cannot be bound."""
+    import numpy as np
+    cfg, rec, _ = models("small")
+    ids = np.random.Generator(np.random.PCG64(5)).integers(0, cfg.vocab, 48).astype(np.int32)
+    ref = orc.OracleExecutor(orc.OracleModel(rec))
+    assert ref.prefill(ids) == 0
+    rc, want = ref.decode_logits()
+    assert rc == 0
+    if not orc.use_xnnpack(2):
+        orc.use_plain_matmul()
+        import pytest
+        pytest.skip("XNNPACK symbols of libtorch_cpu.so not available")
+    try:
+        ex = orc.OracleExecutor(orc.OracleModel(rec))
+        assert ex.prefill(ids) == 0
+        rc, got = ex.decode_logits()
+        assert rc == 0
+    finally:
+        orc.use_plain_matmul()
+    cos = float(np.dot(got, want) / (np.linalg.norm(got) * np.linalg.norm(want)))
+    assert cos >= 0.995 and int(np.argmax(got)) == int(np.argmax(want))
+    # and the hook is gone again: the oracle is bit-identical to before
+    ex = orc.OracleExecutor(orc.OracleModel(rec))
+    assert ex.prefill(ids) == 0
+    assert np.array_equal(ex.decode_logits()[1], want)
