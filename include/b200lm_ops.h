@@ -58,10 +58,10 @@ int B200LmOps_GemmGegluW4(int32_t device, int32_t mode, const uint8_t* gate_pack
  * kv_bf16: bit 0 = bf16 pages (else fp32); bit 1 (decode only) = every query
  * gets its own physical copy of the cache and its own page table, i.e. a
  * batch of independent sequences instead of queries sharing one cache; bit 2
- * (decode only) = the register-resident split kernel (two keys in flight per
- * warp) instead of the default streaming kernel, which fetches K / V in blocks
- * of 16 positions by bulk async copies into a shared-memory ring (the kernel of
- * the wide decode step, csrc/decode_wide.cuh). */
+ * (decode only) = the streaming kernel of the wide decode step
+ * (csrc/decode_wide.cuh: K / V in blocks of 16 positions by bulk async copies
+ * into a shared-memory ring) instead of the register-resident split kernel
+ * (two keys in flight per warp). */
 int B200LmOps_Attention(int32_t device, const float* q, const float* k, const float* v, int32_t t, int32_t s,
                         int32_t hq, int32_t hkv, int32_t hd, int32_t qpos0, int32_t window,
                         int32_t kv_bf16, int32_t nsplit, int32_t repeat, float* out, float* ms_out,

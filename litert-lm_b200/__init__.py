@@ -377,7 +377,7 @@ class ops:
     @staticmethod
     def attention(q: np.ndarray, k: np.ndarray, v: np.ndarray, qpos0: int = 0, window: int = 0, kv_bf16: bool = False,
                   nsplit: int = 1, repeat: int = 1, device: int = 0, private_caches: bool = False,
-                  register_kernel: bool = False) -> Tuple[np.ndarray, float]:
+                  streaming_kernel: bool = False) -> Tuple[np.ndarray, float]:
         q = np.ascontiguousarray(q, dtype=np.float32)
         k = np.ascontiguousarray(k, dtype=np.float32)
         v = np.ascontiguousarray(v, dtype=np.float32)
@@ -386,7 +386,7 @@ class ops:
         out = np.empty_like(q)
         ms = C.c_float(0)
         _call("B200LmOps_Attention", device, _ptr(q), _ptr(k), _ptr(v), t, s, hq, hkv, hd, qpos0, window,
-              int(kv_bf16) | (2 if private_caches else 0) | (4 if register_kernel else 0), nsplit, repeat, _ptr(out),
+              int(kv_bf16) | (2 if private_caches else 0) | (4 if streaming_kernel else 0), nsplit, repeat, _ptr(out),
               C.byref(ms))
         return out, ms.value
 

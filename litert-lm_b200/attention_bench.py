@@ -48,7 +48,7 @@ def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--quick", action="store_true", help="two prefill and two decode shapes only")
     ap.add_argument("--repeat", type=int, default=20)
-    ap.add_argument("--register-kernel", action="store_true", help="decode: the register-resident split kernel instead of the streaming one")
+    ap.add_argument("--streaming-kernel", action="store_true", help="decode: the streaming kernel of the wide decode step instead of the register-resident split kernel")
     args = ap.parse_args()
     graft.build()
     pkg = graft.load_package()
@@ -74,14 +74,15 @@ def main() -> None:
         k = rng.standard_normal((s, HKV, HD), dtype=np.float32)
         v = rng.standard_normal((s, HKV, HD), dtype=np.float32)
         q = rng.standard_normal((batch, HQ, HD), dtype=np.float32)
-        # about two (sequence, kv head, split) work items per SM, splits of at least 256 keys
-        nsplit = max(2, min(64, s // 256, -(-2 * 148 // (batch * HKV))))
+        nsplit = max(2, min(64, s // 256))
+        if args.streaming_kernel:       # one CTA per SM there: about two (sequence, kv head, split) items per SM
+            nsplit = max(2, min(nsplit, -(-2 * 148 // (batch * HKV))))
         _, ms = pkg.ops.attention(q, k, v, nsplit=nsplit, repeat=args.repeat, kv_bf16=True, private_caches=True,
-                                  register_kernel=args.register_kernel)
+                                  streaming_kernel=args.streaming_kernel)
         nbytes = 2.0 * s * HKV * HD * 2 * batch
         gbs = nbytes / (ms * 1e-3) / 1e9
-        print(json.dumps({"op": "decode_attention", "kernel": ("attn_decode_kernel + attn_combine_kernel" if args.register_kernel else
-                                                            "wide_attn_kernel + wide_attn_combine_kernel"), "kv_len": s,
+        print(json.dumps({"op": "decode_attention", "kernel": ("wide_attn_kernel + wide_attn_combine_kernel" if args.streaming_kernel else
+                                                            "attn_decode_kernel + attn_combine_kernel"), "kv_len": s,
                           "batch": batch, "nsplit": nsplit, "page": 256, "kv_dtype": "bf16", "ms": ms, "bytes": nbytes,
                           "roofline": {"bound": "hbm", "achieved": gbs, "peak": hbm, "unit": "GB/s",
                                        "frac": gbs / hbm, "of": src,

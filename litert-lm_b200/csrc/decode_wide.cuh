@@ -98,6 +98,7 @@ struct WideAttnArgs {
   int seq_stride;            // 1: session i has row i of the page table; 0: every query reads sequence 0
   int appended;              // 1: q rows are final (no norm, no rotation) and every K / V row is already in the cache
   float* out_f32;            // nsplit == 1: the same output in fp32 (operator-level callers), optional
+  int ctas_per_sm;           // host-side hint: size the ring so that this many CTAs fit one SM (0 = 1)
 };
 
 template <typename T, int HD>
@@ -107,7 +108,7 @@ __host__ __device__ inline size_t wa_fixed_bytes(int hd, int G) {
 }
 
 template <typename T, int HD, int G>
-__global__ void __launch_bounds__(kWaThreads, 1)
+__global__ void __launch_bounds__(kWaThreads, 2)
 wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
   constexpr int VEC = HD / 32, half = HD / 2;
   constexpr int kStage = wa_stage_bytes<T, HD>();
@@ -346,7 +347,16 @@ template <typename T, int HD, int G>
 inline void launch_wide_attn_t(cudaStream_t st, const ModelDims& d, int nb, size_t smem_optin, WideAttnArgs a) {
   const size_t fixed = wa_fixed_bytes(HD, G);
   const int stage = wa_stage_bytes<T, HD>();
-  const int stages = (int)std::min<size_t>(kWaMaxStages, (smem_optin - 1024 - fixed) / stage);
+  // The loop is a chain of dependent shuffles and exponentials on eight warps, so one CTA alone leaves the SM
+  // mostly idle (about 2 us per block of 16 keys, whatever its bytes): with two CTAs per SM the ring is shallower
+  // but twice as many chains run.
+  int per_sm = std::max(1, a.ctas_per_sm);
+  int stages = 0;
+  for (; per_sm >= 1; --per_sm) {
+    const size_t budget = smem_optin / per_sm - 1024;
+    stages = budget > fixed ? (int)std::min<size_t>(kWaMaxStages, (budget - fixed) / stage) : 0;
+    if (stages >= 2) break;
+  }
   B2_CHECK(stages >= 2, kUnimplemented, "the streaming decode attention does not fit the device's shared memory");
   a.stages = stages;
   const size_t smem = fixed + (size_t)stages * stage;

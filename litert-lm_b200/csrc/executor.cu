@@ -579,7 +579,11 @@ std::unique_ptr<Executor> Executor::create(std::shared_ptr<Model> model, const B
   if (e->decode_mode == B200LM_DECODE_WIDE) {
     int* ws = reinterpret_cast<int*>(e->alloc(sizeof(int) * 3 * kWideMax, true));
     e->wide = WideState{ws, ws + kWideMax, ws + 2 * kWideMax};
-    launch_wide_attn(e->stream, d, 0, e->smem_optin, WideAttnArgs{});
+    {
+      WideAttnArgs prep{};
+      prep.ctas_per_sm = 2;
+      launch_wide_attn(e->stream, d, 0, e->smem_optin, prep);
+    }
     e->wide_part = reinterpret_cast<float*>(
         e->alloc(sizeof(float) * (size_t)e->n_sessions * d.hkv * kWideMaxSplits * d.group() * (d.hd + 2), true));
   }
@@ -1057,9 +1061,9 @@ void Executor::wide_step(int nb, int first) {
   int* err = &dargs.st->err;
   const int mode = B200LM_GEMM_TCGEN05;
   // key splits so that few sessions still fill the SMs: one CTA per (session, kv head, split)
-  const int nsplit = std::max(1, std::min(kWideMaxSplits, n_sms / std::max(1, nb * d.hkv)));
-  // The streaming kernel keeps one CTA per SM busy with deep bulk-copy rings; with well over one (session, kv head)
-  // pair per SM the plain-load kernel, several CTAs resident per SM, overlaps more and has no second wave.
+  const int nsplit = std::max(1, std::min(kWideMaxSplits, 2 * n_sms / std::max(1, nb * d.hkv)));   // two CTAs per SM
+  // The streaming kernel runs two CTAs per SM over key splits; with well over one (session, kv head) pair per SM
+  // the plain-load kernel, several CTAs resident per SM and no splits, was measured faster (64 sessions of the 4B shape).
   const bool stream_attn = nb * d.hkv * 2 <= n_sms * 3;
   const size_t attn_smem = sizeof(float) * ((size_t)(d.group() + 2) * d.hd + (size_t)8 * d.group() * (d.hd + 2));
   pf_embed_norm_kernel<<<nb, kPfThreads, sizeof(float) * d.d, stream>>>(wide.tok, model->embed_rows, model->embed_scale,
@@ -1083,7 +1087,7 @@ void Executor::wide_step(int nb, int first) {
     if (stream_attn) {
     WideAttnArgs wa{pf_qkv, wide.pos, page_table_dev + (size_t)first * pages_per_seq, pages_per_seq, L.is_global, nsplit, 0,
                     L.g_q, L.g_k, model->rope_cos[L.is_global], model->rope_sin[L.is_global], kv_host[li], wide_part, pf_attn, err,
-                    1, 0, nullptr};
+                    1, 0, nullptr, 2};
     launch_wide_attn(stream, d, nb, smem_optin, wa);
     ++*nl;
     if (nsplit > 1) {

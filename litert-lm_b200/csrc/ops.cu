@@ -359,7 +359,7 @@ int B200LmOps_Attention(int32_t device, const float* q, const float* k, const fl
   dm.eps = 1e-6f;
   const bool decode = nsplit > 1;
   const bool priv = decode && (kv_bf16 & 2);     // every query reads its own physical copy of the cache
-  const int kv_bf16_flags = kv_bf16;             // bit 2: the register-resident split kernel instead of the streaming one
+  const int kv_bf16_flags = kv_bf16;             // bit 2: the streaming kernel instead of the register-resident split kernel
   kv_bf16 &= 1;
   const int npages = (s + kPage - 1) / kPage;
   dm.max_ctx = npages * kPage;
@@ -413,12 +413,12 @@ int B200LmOps_Attention(int32_t device, const float* q, const float* k, const fl
   size_t smem_dec = sizeof(float) * ((size_t)(G + 2) * hd + (size_t)kDecWarps * G * (hd + 2));
   raise_dyn_smem(pf_attn_kernel, (size_t)(smem_pf));
   raise_dyn_smem(attn_decode_kernel, (size_t)(smem_dec));
-  // decode: the streaming kernel (K / V blocks by bulk copies into a shared-memory ring) + its combine
+  // decode, on request: the streaming kernel (K / V blocks by bulk copies into a shared-memory ring) + its combine
   DevBuf wpart((size_t)t * hkv * nsplit * G * (hd + 2) * 4, true);
   WideAttnArgs wa{qd.as<float>(), posd.as<int>(), ptab.as<int>(), npages, window > 0 ? 0 : 1, nsplit, 0, nullptr, nullptr, nullptr,
                   nullptr, LayerKv{kp.p, vp.p, nullptr, nullptr}, wpart.as<float>(), nullptr, errw.as<int>(), priv ? 1 : 0, 1,
-                  nullptr};
-  const bool stream_decode = decode && !(kv_bf16_flags & 4);
+                  nullptr, 2};
+  const bool stream_decode = decode && (kv_bf16_flags & 4);
   auto run = [&]() {
     if (stream_decode) {
       launch_wide_attn(nullptr, dm, t, (size_t)prop.sharedMemPerBlockOptin, wa);

@@ -146,6 +146,8 @@ def test_split_kv_decode_attention_matches_oracle(pkg, orc, hq, hkv, hd, batch, 
     # a batch of independent sequences (own cache copy and page table each) gives the same rows, bit for bit
     own, _ = pkg.ops.attention(q, k, v, window=window, kv_bf16=kv_bf16, nsplit=nsplit, private_caches=True)
     assert np.array_equal(own, got)
-    # the register-resident split kernel (what the allocation-free entry point and the per-phase decode run)
-    reg, _ = pkg.ops.attention(q, k, v, window=window, kv_bf16=kv_bf16, nsplit=nsplit, register_kernel=True)
-    assert np.abs(reg - want).max() < 2e-4, np.abs(reg - want).max()
+    # the streaming kernel of the wide decode step on the same request
+    st, _ = pkg.ops.attention(q, k, v, window=window, kv_bf16=kv_bf16, nsplit=nsplit, streaming_kernel=True)
+    assert np.abs(st - want).max() < 2e-4, np.abs(st - want).max()
+    st, _ = pkg.ops.attention(q, k, v, window=window, kv_bf16=kv_bf16, nsplit=nsplit, streaming_kernel=True, private_caches=True)
+    assert np.abs(st - want).max() < 2e-4, np.abs(st - want).max()
