@@ -260,6 +260,20 @@ def run_reference(args, rank: int) -> None:
     }
     if not args.no_xnnpack:
         line["xnnpack"] = xnnpack_leg(args.model, sorted({cores, min(4, cores)}, reverse=True))
+        runs = line["xnnpack"].get("runs") or []
+        best = max(runs, key=lambda r: r["decode_tok_s"]) if runs else None
+        if best and best["decode_tok_s"] > value:
+            # the stronger of the two CPU stand-ins is the arm's value, so that the GPU / CPU ratio is not flattered
+            line["port"] = {"value": value, "prefill_tok_s": prefill_tok_s, "cores": cores}
+            value = best["decode_tok_s"]
+            line["value"] = value
+            line["ms_per_step"] = 1000.0 * n / value
+            line["prefill"] = {"value": best["prefill_tok_s"], "unit": "tok/s"}
+            line["e2e"]["value"] = value
+            line["cpu_baseline"].update({"value": value, "cores": best["threads"], "prefill_tok_s": best["prefill_tok_s"],
+                                         "sample": cpu_sample_text(n) + "; matrix products on XNNPACK (torch-bundled build, "
+                                                   "int8 activations x int8-held int4 weights), the rest the oracle's C"})
+            line["dtype"] = "int4 values as int8 weights x dynamically quantised int8 activations (XNNPACK), fp32 elsewhere (CPU)"
     print(json.dumps(line), flush=True)
 
 
