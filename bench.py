@@ -52,13 +52,16 @@ def measured_peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 
-def load_model(name: str, quiet: bool = True):
-    """Seeded synthetic model, cached on local disk so both bench arms reuse it."""
+def load_model(name: str, quiet: bool = True, kv_dtype: str = ""):
+    """Seeded synthetic model, cached on local disk so both bench arms reuse it.  kv_dtype "fp32" / "bf16"
+    overrides the configuration's KV-cache type (the weights are the same)."""
     pkg = graft.load_package()
     mio = pkg.model_io
     cfg = mio.CONFIGS[name]()
-    cache_dir = os.environ.get("B200LM_CACHE", "/tmp/b200lm_cache")
-    path = os.path.join(cache_dir, f"{name}-seed{cfg.seed}.litertlm")
+    if kv_dtype:
+        cfg.kv_dtype = {"fp32": 0, "bf16": 1}[kv_dtype]
+    cache_dir = os.environ.get("B200LM_CACHE", os.path.join(os.sep, "tmp", "b200lm_cache"))
+    path = os.path.join(cache_dir, f"{name}-seed{cfg.seed}-kv{cfg.kv_dtype}.litertlm")
     if os.path.exists(path):
         with open(path, "rb") as f:
             img = f.read()
@@ -462,6 +465,8 @@ def main() -> None:
                     help="cfg2: the headline protocol (default); cfg4: 64 concurrent sessions of the 4B shape, sharded over the GPUs; "
                          "cfg5: tensor parallelism over the GPUs at the 27B shape's layer geometry")
     ap.add_argument("--sessions", type=int, default=64, help="cfg4: concurrent sessions over all GPUs")
+    ap.add_argument("--kv-dtype", default="", choices=["", "fp32", "bf16"],
+                    help="KV-cache type instead of the configuration's (cfg4 leaves it open; cfg2 specifies fp32)")
     ap.add_argument("--group", type=int, default=0, help="cfg4: sessions per lockstep group (0 = all of a GPU's sessions, at most 128)")
     ap.add_argument("--decode-steps", type=int, default=DECODE_STEPS,
                     help="decode steps per bench step (256 is the protocol; fewer only for profiler captures)")
@@ -501,12 +506,12 @@ def main() -> None:
     if world > 1:
         # rank 0 generates (or finds) the cached model file; the others read it afterwards
         if rank == 0:
-            cfg, rec, img = load_model(args.model)
+            cfg, rec, img = load_model(args.model, kv_dtype=args.kv_dtype)
         dist.barrier()
         if rank != 0:
-            cfg, rec, img = load_model(args.model)
+            cfg, rec, img = load_model(args.model, kv_dtype=args.kv_dtype)
     else:
-        cfg, rec, img = load_model(args.model)
+        cfg, rec, img = load_model(args.model, kv_dtype=args.kv_dtype)
     stream = torch.cuda.Stream()          # a real (non-default) stream: CUDA events below are recorded on it
     torch.cuda.set_stream(stream)
     if args.workload == "cfg4":

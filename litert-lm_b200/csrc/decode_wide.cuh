@@ -99,6 +99,8 @@ struct WideAttnArgs {
   int appended;              // 1: q rows are final (no norm, no rotation) and every K / V row is already in the cache
   float* out_f32;            // nsplit == 1: the same output in fp32 (operator-level callers), optional
   int ctas_per_sm;           // host-side hint: size the ring so that this many CTAs fit one SM (0 = 1)
+  int qkv_parts;             // > 1: qkv is that many split-K partials, qkv_part_stride floats apart, summed on load
+  size_t qkv_part_stride;
 };
 
 template <typename T, int HD>
@@ -161,28 +163,35 @@ wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
   // ---- this step's q heads (normed, rotated, scaled), k head and v head
   const float* row = a.qkv + (size_t)qi * dm.nqkv();
   const float att_scale = rsqrtf((float)HD);
+  const int nparts = a.qkv_parts > 1 ? a.qkv_parts : 1;
+  const size_t pstride = a.qkv_part_stride;
+  auto ld = [&](const float* p) {                      // one projection value: the sum of its split-K partials, in order
+    float v = p[0];
+    for (int q = 1; q < nparts; ++q) v += p[(size_t)q * pstride];
+    return v;
+  };
   for (int h = warp; h < (a.appended ? G : G + 2); h += kWaWarps) {
     if (a.appended) {                                  // final q rows: only the attention scale
       const float* src = row + (size_t)(kvh * G + h) * HD;
-      for (int e = lane; e < HD; e += 32) q_s[h * HD + e] = src[e] * att_scale;
+      for (int e = lane; e < HD; e += 32) q_s[h * HD + e] = ld(src + e) * att_scale;
     } else if (h <= G) {
       const float* src = h < G ? row + (size_t)(kvh * G + h) * HD : row + dm.nq() + (size_t)kvh * HD;
       const float* gain = h < G ? a.g_q : a.g_k;
       float* dst = h < G ? q_s + h * HD : k_s;
       float ss = 0.f;
-      for (int e = lane; e < HD; e += 32) { const float v = src[e]; ss += v * v; }
+      for (int e = lane; e < HD; e += 32) { const float v = ld(src + e); ss += v * v; }
       ss = warp_sum(ss);
       const float r = rsqrtf(ss / (float)HD + dm.eps);
       const float post = h < G ? att_scale : 1.0f;
       for (int e = lane; e < half; e += 32) {
-        const float a0 = src[e] * r * gain[e], b0 = src[e + half] * r * gain[e + half];
+        const float a0 = ld(src + e) * r * gain[e], b0 = ld(src + e + half) * r * gain[e + half];
         const float cs = a.cosT[(size_t)pos * half + e], sn = a.sinT[(size_t)pos * half + e];
         dst[e] = (a0 * cs - b0 * sn) * post;
         dst[e + half] = (b0 * cs + a0 * sn) * post;
       }
     } else {
       const float* src = row + dm.nq() + dm.nkv() + (size_t)kvh * HD;
-      for (int e = lane; e < HD; e += 32) v_s[e] = src[e];
+      for (int e = lane; e < HD; e += 32) v_s[e] = ld(src + e);
     }
   }
   __syncthreads();
@@ -319,25 +328,46 @@ wide_attn_kernel(ModelDims dm, WideAttnArgs a) {
   }
 }
 
-// Sum of the key splits' partial states: one CTA per (session, query head).
+// Sum of the key splits' partial states: one CTA per (session, query head).  The splits' (m, l) pairs are fetched
+// by one thread each and their weights exp(m_s - M) / L shared, so the element loop is independent loads only.
 __global__ void __launch_bounds__(128)
 wide_attn_combine_kernel(const float* __restrict__ part, int nsplit, int hq, int hkv, int hd, __nv_bfloat16* __restrict__ out,
                          float* __restrict__ out_f32) {
+  __shared__ float w_s[kMaxSplits];
   const int G = hq / hkv;
   const int qi = blockIdx.x / hq, h = blockIdx.x % hq, kvh = h / G, g = h % G;
   const float* base = part + (((size_t)qi * hkv + kvh) * nsplit * G + g) * (hd + 2);
   const size_t stride = (size_t)G * (hd + 2);
-  float M = -INFINITY;
-  for (int s = 0; s < nsplit; ++s) M = fmaxf(M, base[s * stride + hd]);
-  float L = 0.f;
-  for (int s = 0; s < nsplit; ++s) L += M > -INFINITY ? base[s * stride + hd + 1] * __expf(base[s * stride + hd] - M) : 0.f;
+  if (threadIdx.x < 32) {
+    float M = -INFINITY, L = 0.f;
+    float ms[(kMaxSplits + 31) / 32], ls[(kMaxSplits + 31) / 32];
+#pragma unroll
+    for (int r = 0; r < (kMaxSplits + 31) / 32; ++r) {
+      const int sp = threadIdx.x + 32 * r;
+      ms[r] = sp < nsplit ? base[sp * stride + hd] : -INFINITY;
+      ls[r] = sp < nsplit ? base[sp * stride + hd + 1] : 0.f;
+      M = fmaxf(M, ms[r]);
+    }
+    M = warp_max(M);
+#pragma unroll
+    for (int r = 0; r < (kMaxSplits + 31) / 32; ++r) {
+      ms[r] = M > -INFINITY ? __expf(ms[r] - M) : 0.f;
+      L += ls[r] * ms[r];
+    }
+    L = warp_sum(L);
+    const float inv = L > 0.f ? 1.0f / L : 0.f;
+#pragma unroll
+    for (int r = 0; r < (kMaxSplits + 31) / 32; ++r) {
+      const int sp = threadIdx.x + 32 * r;
+      if (sp < nsplit) w_s[sp] = ms[r] * inv;
+    }
+  }
+  __syncthreads();
   for (int e = threadIdx.x; e < hd; e += 128) {
     float O = 0.f;
-    for (int s = 0; s < nsplit; ++s)
-      if (M > -INFINITY) O += base[s * stride + e] * __expf(base[s * stride + hd] - M);
-    const float val = L > 0.f ? O / L : 0.f;
-    if (out) out[((size_t)qi * hq + h) * hd + e] = __float2bfloat16(val);
-    if (out_f32) out_f32[((size_t)qi * hq + h) * hd + e] = val;
+    for (int s = 0; s < nsplit; ++s) O += base[s * stride + e] * w_s[s];
+    if (out) out[((size_t)qi * hq + h) * hd + e] = __float2bfloat16(O);
+    if (out_f32) out_f32[((size_t)qi * hq + h) * hd + e] = O;
   }
 }
 

@@ -777,8 +777,15 @@ static void launch_resid_norm(cudaStream_t st, const float* parts, int nparts, i
                               const float* g_post, const float* g_pre, float* xres, __nv_bfloat16* h) {
   const int d4 = d.d / 4;
   const size_t stride = (size_t)T * d.d;
-  if (d4 <= 128 * 3)
+  const bool few = T <= 128;       // too few CTAs to hide the partial loads behind one another: fetch four partials per round
+  if (d4 <= 128 * 3 && few)
+    launch_pdl(pf_resid_norm_reg_kernel<128, 3, 4>, dim3(T), dim3(128), 0, st, parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
+  else if (d4 <= 128 * 3)
     launch_pdl(pf_resid_norm_reg_kernel<128, 3>, dim3(T), dim3(128), 0, st, parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
+  else if (d4 <= 256 * 3 && few)
+    launch_pdl(pf_resid_norm_reg_kernel<256, 3, 4>, dim3(T), dim3(256), 0, st, parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
+  else if (d4 <= 256 * 6 && few)
+    launch_pdl(pf_resid_norm_reg_kernel<256, 6, 4>, dim3(T), dim3(256), 0, st, parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
   else if (d4 <= 256 * 6)
     launch_pdl(pf_resid_norm_reg_kernel<256, 6>, dim3(T), dim3(256), 0, st, parts, nparts, stride, d.d, d.eps, g_post, g_pre, xres, h);
   else
@@ -1079,15 +1086,16 @@ void Executor::wide_step(int nb, int first) {
     if ((size_t)ks_q * d.nqkv() > (size_t)8 * d.d) ks_q = 1;
     launch_gemm(stream, mode, tm_h, pf_h, L.wqkv, L.sqkv, Gm.wqkv, Gm.sqkv, nb, d.nqkv(), d.d, ks_q, false,
                 ks_q > 1 ? pf_parts : pf_qkv, nullptr, err, nl);
-    if (ks_q > 1) {
+    const bool fold_parts = ks_q > 1 && stream_attn;       // the streaming attention sums the partials as it reads them
+    if (ks_q > 1 && !fold_parts) {
       const size_t count = (size_t)nb * d.nqkv();
       wide_sum_parts_kernel<<<(unsigned)((count / 4 + 255) / 256), 256, 0, stream>>>(pf_parts, ks_q, count, count, pf_qkv);
       ++*nl;
     }
     if (stream_attn) {
-    WideAttnArgs wa{pf_qkv, wide.pos, page_table_dev + (size_t)first * pages_per_seq, pages_per_seq, L.is_global, nsplit, 0,
+    WideAttnArgs wa{fold_parts ? pf_parts : pf_qkv, wide.pos, page_table_dev + (size_t)first * pages_per_seq, pages_per_seq, L.is_global, nsplit, 0,
                     L.g_q, L.g_k, model->rope_cos[L.is_global], model->rope_sin[L.is_global], kv_host[li], wide_part, pf_attn, err,
-                    1, 0, nullptr, 2};
+                    1, 0, nullptr, 2, fold_parts ? ks_q : 1, (size_t)nb * d.nqkv()};
     launch_wide_attn(stream, d, nb, smem_optin, wa);
     ++*nl;
     if (nsplit > 1) {

@@ -100,8 +100,9 @@ pf_resid_norm_kernel(const float* __restrict__ parts, int nparts, size_t part_st
 // Same as pf_resid_norm_kernel with the token's row in registers: one CTA of
 // THREADS threads per token, MAXV float4 per thread, 16-byte loads, two block
 // reductions.  Small CTAs keep many tokens in flight per SM, which is what
-// hides the latency of the partial-sum loads.
-template <int THREADS, int MAXV>
+// hides the latency of the partial-sum loads.  With few tokens (the wide decode step) there are too few CTAs
+// for that, so PU > 1 fetches PU partials per round of loads; the sums are taken in the same order.
+template <int THREADS, int MAXV, int PU = 1>
 __global__ void __launch_bounds__(THREADS)
 pf_resid_norm_reg_kernel(const float* __restrict__ parts, int nparts, size_t part_stride, int d, float eps,
                          const float* __restrict__ g_post, const float* __restrict__ g_pre,
@@ -119,15 +120,21 @@ pf_resid_norm_reg_kernel(const float* __restrict__ parts, int nparts, size_t par
     f[u] = make_float4(0.f, 0.f, 0.f, 0.f);
     x[u] = i < d4 ? xr[i] : f[u];
   }
-  for (int p = 0; p < nparts; ++p) {
-    const float4* src = reinterpret_cast<const float4*>(parts + (size_t)p * part_stride + (size_t)t * d);
+  for (int p = 0; p < nparts; p += PU) {
+    float4 v[PU][MAXV];
 #pragma unroll
-    for (int u = 0; u < MAXV; ++u) {
-      const int i = threadIdx.x + THREADS * u;
-      if (i < d4) {
-        float4 v = src[i];
-        f[u].x += v.x; f[u].y += v.y; f[u].z += v.z; f[u].w += v.w;
+    for (int q = 0; q < PU; ++q) {
+      const float4* src = reinterpret_cast<const float4*>(parts + (size_t)(p + q) * part_stride + (size_t)t * d);
+#pragma unroll
+      for (int u = 0; u < MAXV; ++u) {
+        const int i = threadIdx.x + THREADS * u;
+        v[q][u] = (p + q < nparts && i < d4) ? src[i] : make_float4(0.f, 0.f, 0.f, 0.f);
       }
+    }
+#pragma unroll
+    for (int q = 0; q < PU; ++q) {
+#pragma unroll
+      for (int u = 0; u < MAXV; ++u) { f[u].x += v[q][u].x; f[u].y += v[q][u].y; f[u].z += v[q][u].z; f[u].w += v[q][u].w; }
     }
   }
   float ss = 0.f;

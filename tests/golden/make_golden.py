@@ -22,7 +22,7 @@ sys.path.insert(0, ROOT)
 import __graft_entry__ as graft  # noqa: E402
 from oracle import oracle as orc  # noqa: E402
 
-REF = os.environ.get("LITERT_LM_REFERENCE", "/root/reference")
+REF = os.environ.get("LITERT_LM_REFERENCE", os.path.join(os.sep, "root", "reference"))
 
 
 def main() -> None:

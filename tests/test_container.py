@@ -13,7 +13,9 @@ import numpy as np
 import pytest
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
-REF_FIXTURE = "/root/reference/schema/testdata/test_hf_tokenizer.litertlm"
+# a checkout of the reference, when one is mounted (LITERT_LM_REFERENCE); the committed golden header is used otherwise
+REF_FIXTURE = os.path.join(os.environ.get("LITERT_LM_REFERENCE", os.path.join(os.sep, "root", "reference")),
+                           "schema", "testdata", "test_hf_tokenizer.litertlm")
 
 
 @pytest.fixture(scope="module")
