@@ -27,19 +27,30 @@ def build(force: bool = False) -> str:
 _xnnb = None
 
 
+def build_xnnpack_baseline() -> str:
+    """Compiles xnn_baseline.c against torch's copy of xnnpack.h (no torch import: the header path comes from the
+    package's location).  Raises when the header or the compiler is missing."""
+    import importlib.util
+    spec = importlib.util.find_spec("torch")
+    if spec is None or not spec.origin:
+        raise RuntimeError("torch is not installed: no xnnpack.h to compile against")
+    inc = os.path.join(os.path.dirname(spec.origin), "include")
+    out = os.path.join(_HERE, "libxnnb.so")
+    src = os.path.join(_HERE, "xnn_baseline.c")
+    if not os.path.exists(out) or os.path.getmtime(out) < os.path.getmtime(src):
+        subprocess.check_call(["make", "-C", _HERE, "-B", "libxnnb.so", f"TORCH_INC={inc}"], stdout=subprocess.DEVNULL,
+                              stderr=subprocess.DEVNULL)
+    return out
+
+
 def use_xnnpack(threads: int) -> bool:
-    """Timing baseline only: routes the oracle's matrix products through XNNPACK's int4-weight /
-    dynamically-quantised-int8-activation fully-connected operator (the XNNPACK build inside torch) on a pool
-    of `threads` workers, and limits the OpenMP parts to the same count.  False when it cannot be set up."""
+    """Timing baseline only: routes the oracle's matrix products through XNNPACK's fully-connected operator with
+    dynamically quantised int8 activations (the XNNPACK build inside torch) on a pool of `threads` workers, and
+    limits the OpenMP parts to the same count.  False when it cannot be set up."""
     global _xnnb
     try:
+        out = build_xnnpack_baseline()
         import torch  # noqa: F401  (loads libtorch_cpu.so, which exports the xnn_* symbols)
-        inc = os.path.join(os.path.dirname(torch.__file__), "include")
-        out = os.path.join(_HERE, "libxnnb.so")
-        src = os.path.join(_HERE, "xnn_baseline.c")
-        if not os.path.exists(out) or os.path.getmtime(out) < os.path.getmtime(src):
-            subprocess.check_call(["make", "-C", _HERE, "-B", "libxnnb.so", f"TORCH_INC={inc}"], stdout=subprocess.DEVNULL,
-                                  stderr=subprocess.DEVNULL)
         if _xnnb is None:
             _xnnb = C.CDLL(out, mode=C.RTLD_GLOBAL)
             _xnnb.xnnb_init.argtypes = [C.c_int, C.c_char_p]
