@@ -339,8 +339,10 @@ def run_cfg4(args, pkg, cfg, img, stream, rank: int, world: int, local_rank: int
     sampler = ClockSampler(local_rank)
     sampler.start()
     barrier()
+    launches0 = sum(ex.GetLaunchCount() for ex in execs)
     res = [step() for _ in range(max(1, min(args.steps, 3)))]
     barrier()
+    launches = sum(ex.GetLaunchCount() for ex in execs) - launches0       # this rank's kernels in the timed region
     clocks = sampler.finish()
     n = len(res)
     tok, (pf_ms, dec_ms) = pkg.sharding.reduce_throughput(n * len(mine) * DECODE_STEPS, [sum(r[0] for r in res), sum(r[1] for r in res)])
@@ -368,6 +370,7 @@ def run_cfg4(args, pkg, cfg, img, stream, rank: int, world: int, local_rank: int
                    "kv_capacity_per_session": cap},
         "prefill": {"value": world * n * len(mine) * PREFILL_TOKENS / (pf_ms / 1e3), "unit": "tok/s"},
         "decode_ms_per_group_step": dec_ms / steps_per_gpu,
+        "gpu_launches": int(launches),
         "clocks": clocks,
         "roofline": {"bound": "hbm", "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s", "frac": achieved / peaks["hbm_gbs"],
                      "traffic": None, "of": peaks["source"], "algorithmic_bytes_per_group_step": per_step,
