@@ -68,7 +68,7 @@ def main() -> None:
                               "head_dim": HD, "dtype": "bf16 operands, fp32 accumulate", "ms": ms, "flops": flops,
                               "roofline": {"bound": "tensor", "achieved": tf, "peak": tensor, "unit": "TFLOP/s",
                                            "frac": tf / tensor, "of": src}}), flush=True)
-    shapes = ((1024, 1), (32768, 64)) if args.quick else tuple((s, b) for s in (1024, 4096, 16384, 32768)
+    shapes = ((1024, 1), (32768, 64)) if args.quick else tuple((s, b) for s in (1024, 2048, 4096, 8192, 16384, 32768)
                                                               for b in (1, 4, 16, 64))
     for s, batch in shapes:
         k = rng.standard_normal((s, HKV, HD), dtype=np.float32)
